@@ -1,0 +1,141 @@
+/* C ABI of libmomoe_b200.so: the B200 (sm_100a) implementation of the MoMoE layer hot path.
+ *
+ * Each entry point replaces one piece of the reference's Python/Triton path; the reference location it
+ * stands in for is cited as file:line relative to the reference project root.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless stated otherwise; bf16 tensors are passed as `const void*`;
+ *  - no entry point allocates device memory or synchronises the host with the device; all work is queued on
+ *    the `stream` argument (a cudaStream_t passed as void*);
+ *  - return value: 0 on success, negative when the arguments are rejected on the host (nothing is launched);
+ *  - problems that only the device can detect (a wait that ran out, a token without exactly K experts) are
+ *    written as a positive code into the caller's int32 `status` word, which must be zeroed by the caller;
+ *  - "expert-major" buffers hold one row per (token, expert) pair, grouped by expert in ascending expert id and,
+ *    inside an expert, ascending token id.  Every expert segment starts at a multiple of 128 rows (padding rows
+ *    are zero), so every 128-row tile belongs to exactly one expert.  `momoe_sorted_rows_capacity` gives the
+ *    number of rows such a buffer must have.
+ */
+#ifndef MOMOE_B200_H
+#define MOMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* momoe_stream_t;
+
+/* Routing plan of one forward pass: dimensions plus the device tables written by momoe_build_permutation. */
+typedef struct momoe_plan {
+    int32_t M;                   /* tokens (B*S) */
+    int32_t N;                   /* experts */
+    int32_t K;                   /* experts per token, shared experts included */
+    int32_t D;                   /* embedding dim */
+    int32_t H;                   /* intermediate dim */
+    int32_t reserved;
+    int64_t rows_capacity;       /* rows of every expert-major buffer (momoe_sorted_rows_capacity) */
+    const int32_t* sched;        /* int32[8]: [0] 128-row tiles in use, [1] tiles whose a,b are saved, [2] padded rows */
+    const int32_t* tile_expert;  /* int32[momoe_tile_capacity]: expert of each tile */
+    const int32_t* pad_off;      /* int32[N+1]: first padded row of each expert */
+    const int32_t* row_token;    /* int32[rows_capacity]: token of each padded row, -1 on padding rows */
+    const float* row_weight;     /* float[rows_capacity]: routing weight of each padded row, 0 on padding rows */
+    const int32_t* pos_MK;       /* int32[M*K]: padded row of token m's k-th expert (ascending expert id) */
+    int32_t* status;             /* device int32 error word, zeroed by the caller */
+} momoe_plan_t;
+
+int momoe_version(void);
+
+/* Rows / tiles an expert-major buffer needs for M tokens, K experts each, N experts (host arithmetic only). */
+int64_t momoe_sorted_rows_capacity(int32_t M, int32_t K, int32_t N);
+int64_t momoe_tile_capacity(int32_t M, int32_t K, int32_t N);
+
+/* Router after the gate GEMM: fp32 softmax over the N-Ks gating experts and over the Ks shared experts,
+ * top-(K-Ks) of probability + bias (ties: lowest expert id), renormalisation.
+ * Replaces momoe/topk_router.py:96-120.
+ *   logits_MN   bf16 [M,N] contiguous;  biases_N fp32 [N] (entries of shared experts are not read)
+ *   topk_idx_MK int32 [M,K] ascending expert ids (shared experts last);  topk_w_MK fp32 [M,K] their weights
+ *   optional dense outputs (all NULL or all non-NULL): mask_NM int32 [N,M], s_MN fp32 [M,N] (the reference's
+ *   s_NM is its transpose view), s_postsoft_MN fp32 [M,N], Ng_M fp32 [M], Ks_M fp32 [M]. */
+int momoe_route_topk(const void* logits_MN, const float* biases_N, int32_t M, int32_t N, int32_t K, int32_t Ks,
+                     int32_t* topk_idx_MK, float* topk_w_MK, int32_t* mask_NM, float* s_MN, float* s_postsoft_MN,
+                     float* Ng_M, float* Ks_M, momoe_stream_t stream);
+
+/* Compact form of an external router's dense mask_NM / s_NM (any strides, in elements).
+ * Replaces the mask scan of momoe/momoe.py:760-815.  A token without exactly K experts sets *status. */
+int momoe_topk_from_mask(const int32_t* mask_NM, int64_t mask_stride_n, int64_t mask_stride_m, const float* s_NM,
+                         int64_t s_stride_n, int64_t s_stride_m, int32_t M, int32_t N, int32_t K,
+                         int32_t* topk_idx_MK, float* topk_w_MK, int32_t* status, momoe_stream_t stream);
+
+/* Expert-major permutation from the compact routing.  Replaces momoe/momoe.py:821-842 (find_used_experts).
+ * Outputs identical to the reference: sizes_N int64 [N], cumsums_N1 int32 [N+1], idx_Msum int32 [M*K],
+ * which_Msum int32 [M*K] (slot = rank of the expert among the token's experts).  Plus the padded tables of
+ * momoe_plan_t.  save_rows = int(M*K*save_percent/100) (momoe/momoe.py:251); sched[1] receives the number of
+ * leading tiles that lie entirely below it (the tile rule of momoe/momoe.py:486). */
+size_t momoe_permutation_workspace_bytes(int32_t M, int32_t N, int32_t K);
+int momoe_build_permutation(const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N, int32_t K,
+                            int64_t save_rows, int64_t* sizes_N, int32_t* cumsums_N1, int32_t* idx_Msum,
+                            int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert, int32_t* sched,
+                            int32_t* row_token, float* row_weight, int32_t* pos_MK, int64_t rows_capacity,
+                            void* workspace, size_t workspace_bytes, int32_t* status, momoe_stream_t stream);
+
+/* dst[r,:] = src[row_token[r],:] (zeros on padding rows), bf16, `cols` columns (multiple of 8).
+ * Replaces the row gathers of momoe/momoe.py:116-118 and :298-350. */
+int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
+                      momoe_stream_t stream);
+
+/* dst[m,:] = bf16( sum_k float(src_sorted[pos_MK[m,k],:]) ).  Replaces the K-slab scatter + `sum(dim=0)` of
+ * momoe/momoe.py:234-237,290 and :679-681,754. */
+int momoe_combine_rows(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
+                       momoe_stream_t stream);
+
+/* Up/gate grouped GEMM + SwiGLU: a = x W1[e][:, :H], b = x W1[e][:, H:], h = bf16(a * b * sigmoid(b)).
+ * Replaces momoe/momoe.py:69-152.
+ *   ab_mode 0: only h is written.
+ *   ab_mode 1: h, and bf16 a,b of the saved tiles (tile < sched[1]) at row tile*128 of a_out/b_out.
+ *   ab_mode 2: recomputation for the backward pass: only tiles >= sched[1] are processed, a,b go to row
+ *              (tile - sched[1])*128 of a_out/b_out; h_sorted may be NULL. */
+int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted, const void* W1_ND2H, void* h_sorted,
+                    void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream);
+
+/* Down grouped GEMM with the routing weight in the epilogue: y_sorted[r,:] = bf16(w[r] * (h[r,:] W2[e])).
+ * Replaces momoe/momoe.py:161-237. */
+int momoe_down_scale(const momoe_plan_t* plan, const void* h_sorted, const void* W2_NHD, void* y_sorted,
+                     momoe_stream_t stream);
+
+/* Backward of the down projection fused with the SwiGLU backward.  Replaces momoe/momoe.py:421-535 and the
+ * G_s reduction of :684-703.  With Gh = g_sorted W2[e]^T (g_sorted is the UN-weighted gathered upstream
+ * gradient) and a,b taken from the saved buffers (tile < sched[1]) or the recomputed ones:
+ *   gz_sorted [rows,2H] = bf16[ w*Gh*b*sig(b) | w*Gh*a*sig(b)*(1+b*(1-sig(b))) ]
+ *   hs_sorted [rows,H]  = bf16( w * bf16(a*b*sig(b)) )           (left operand of the W2 gradient)
+ *   gs_part   [rows,ceil(H/128)] fp32 partial sums of <Gh, bf16(a*b*sig(b))> (their sum is dL/ds). */
+int momoe_dgrad2_swiglu_bwd(const momoe_plan_t* plan, const void* g_sorted, const void* W2_NHD,
+                            const void* a_saved, const void* b_saved, const void* a_recomp, const void* b_recomp,
+                            void* gz_sorted, void* hs_sorted, float* gs_part, momoe_stream_t stream);
+
+/* gx_sorted = bf16(gz_sorted W1[e]^T).  Replaces the GEMM of momoe/momoe.py:612-681. */
+int momoe_dgrad1(const momoe_plan_t* plan, const void* gz_sorted, const void* W1_ND2H, void* gx_sorted,
+                 momoe_stream_t stream);
+
+/* dW[e] = bf16( A_e^T B_e ) over the rows of expert e (fp32 accumulation; zero for experts without tokens).
+ * A: [rows, X], B: [rows, Y] expert-major bf16.  Replaces momoe/momoe.py:356-412. */
+int momoe_wgrad(const momoe_plan_t* plan, const void* a_sorted, int32_t X, const void* b_sorted, int32_t Y,
+                void* dW_NXY, momoe_stream_t stream);
+
+/* Dense G_s_NM fp32 [N,M] contiguous (zero where unselected) from the per-row partial sums.
+ * Replaces the zero-init + atomics of momoe/momoe.py:721,699-703. */
+int momoe_scatter_gs(const momoe_plan_t* plan, const float* gs_part, int32_t n_part, float* G_s_NM,
+                     momoe_stream_t stream);
+
+/* Router backward before the two gate GEMMs: renormalisation backward then softmax backward, separately for
+ * the gating and the shared group, rounded to bf16.  Replaces momoe/topk_router.py:11-56.
+ *   G_s: dL/ds addressed as G_s[n*gs_stride_n + m*gs_stride_m]; output G_logits_MN bf16 [M,N]. */
+int momoe_router_backward(const float* G_s, int64_t gs_stride_n, int64_t gs_stride_m, const float* s_postsoft_MN,
+                          const float* s_MN, const float* Ng_M, const float* Ks_M, const int32_t* mask_NM,
+                          int32_t M, int32_t N, int32_t Ks, void* G_logits_MN, momoe_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOMOE_B200_H */

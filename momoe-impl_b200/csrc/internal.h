@@ -1,0 +1,41 @@
+// Internal declarations shared by the translation units of libmomoe_b200.so.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace momoe {
+
+constexpr int TILE_M = 128;  // rows of one expert-major tile; every expert segment is padded to a multiple
+constexpr int TILE_K = 64;   // bf16 elements per 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+// Status codes returned by the C entry points (negative: rejected on the host).
+enum : int {
+    MOMOE_OK = 0,
+    MOMOE_ERR_ARG = -1,        // bad pointer / size / alignment
+    MOMOE_ERR_UNSUPPORTED = -2,  // shape outside what the kernels handle
+    MOMOE_ERR_CUDA = -3,       // a CUDA runtime / driver call failed
+    MOMOE_ERR_TOO_LARGE = -4,  // exceeds a fixed capacity
+};
+// Codes written by kernels into the caller's device status word.
+enum : int {
+    DEV_TIMEOUT_PRODUCER = 101,
+    DEV_TIMEOUT_MMA = 102,
+    DEV_TIMEOUT_EPILOGUE = 103,
+    DEV_BAD_TOPK_COUNT = 201,   // a token does not have exactly K experts in mask_NM
+    DEV_BAD_EXPERT_ID = 202,
+};
+
+// sched[] layout (device int32[8]) written by the permutation builder and read by every later kernel.
+enum : int { SCHED_N_TILES = 0, SCHED_N_SAVED_TILES = 1, SCHED_PAD_ROWS = 2, SCHED_WORDS = 8 };
+
+int sm_count();
+int encode_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                   uint32_t box_cols);
+int encode_tmap_3d(CUtensorMap* m, const void* base, uint64_t d2, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                   uint32_t box_cols);
+
+}  // namespace momoe

@@ -1,0 +1,576 @@
+// Router (softmax + top-k with bias), expert-major permutation, row gather / combine, and the small
+// backward helpers.  All of this is HBM-bound integer / byte work: warp-level kernels, 128-bit accesses.
+#include <cmath>
+#include <cstring>
+
+#include "internal.h"
+#include "../../include/momoe_b200.h"
+
+namespace momoe {
+
+constexpr int MAX_EXPERTS = 1024;
+constexpr int MAX_TOPK = 32;
+constexpr int CHUNK_TOKENS = 64;  // tokens one warp ranks in the permutation passes
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Butterfly in the order 16, 8, 4, 2, 1: the order torch's warp softmax uses, so the fp32 sum is identical.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ------------------------------------------------------------------------------------------------ router
+// One warp per token.  Element j of the gating group lives in lane j % 32, slot j / 32 (the layout of
+// torch's warp softmax), so max / exp / sum are evaluated in the same order and p is bit-identical.
+template <int NPL>  // gating elements per lane
+__global__ void route_topk_kernel(const __nv_bfloat16* __restrict__ logits, const float* __restrict__ biases, int M,
+                                  int N, int K, int Ks, int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                  int* __restrict__ mask_NM, float* __restrict__ s_MN,
+                                  float* __restrict__ s_postsoft_MN, float* __restrict__ Ng_M,
+                                  float* __restrict__ Ks_M) {
+    const int lane = threadIdx.x & 31;
+    const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (m >= M) return;
+    const int Ng = N - Ks;
+    const int Kg = K - Ks;
+    const __nv_bfloat16* row = logits + static_cast<size_t>(m) * N;
+
+    float p[NPL];
+    float score[NPL];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+        const int j = lane + i * 32;
+        p[i] = (j < Ng) ? __bfloat162float(row[j]) : -INFINITY;
+        mx = fmaxf(mx, p[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+        p[i] = expf(p[i] - mx);
+        sum += p[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+        const int j = lane + i * 32;
+        p[i] = p[i] / sum;
+        score[i] = (j < Ng) ? p[i] + biases[j] : -INFINITY;
+    }
+
+    // top-Kg by repeated warp arg-max; equal scores resolve to the lowest expert id
+    uint32_t picked = 0;  // bit i: slot i of this lane is selected
+    for (int k = 0; k < Kg; ++k) {
+        float bv = -INFINITY;
+        int bj = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int j = lane + i * 32;
+            const bool free_slot = ((picked >> i) & 1u) == 0 && j < Ng;
+            if (free_slot && (score[i] > bv || bj == 0x7fffffff)) {  // slots ascend in j, so ties keep the lower j
+                bv = score[i];
+                bj = j;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oj = __shfl_xor_sync(0xffffffffu, bj, o);
+            if (oj != 0x7fffffff && (bj == 0x7fffffff || ov > bv || (ov == bv && oj < bj))) {
+                bv = ov;
+                bj = oj;
+            }
+        }
+        if (bj != 0x7fffffff && (bj & 31) == lane) picked |= 1u << (bj >> 5);
+    }
+
+    // renormalise the selected probabilities (sum in ascending expert id)
+    float ng = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+        const uint32_t bal = __ballot_sync(0xffffffffu, (picked >> i) & 1u);
+        for (uint32_t b = bal; b != 0; b &= b - 1) {
+            const int src = __ffs(b) - 1;
+            ng += __shfl_sync(0xffffffffu, p[i], src);
+        }
+    }
+
+    // shared experts: softmax over the last Ks logits (lane = index inside the group)
+    float ps = 0.0f, ks_sum = 0.0f;
+    if (Ks > 0) {
+        float l = (lane < Ks) ? __bfloat162float(row[Ng + lane]) : -INFINITY;
+        const float smx = warp_max(l);
+        const float e = expf(l - smx);
+        const float ssum = warp_sum(e);
+        ps = e / ssum;
+        ks_sum = 0.0f;
+        for (int j = 0; j < Ks; ++j) ks_sum += __shfl_sync(0xffffffffu, ps, j);
+    }
+
+    // compact outputs, ascending expert id
+    int base = 0;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+        const bool sel = (picked >> i) & 1u;
+        const uint32_t bal = __ballot_sync(0xffffffffu, sel);
+        if (sel) {
+            const int slot = base + __popc(bal & ((1u << lane) - 1u));
+            topk_idx[static_cast<size_t>(m) * K + slot] = lane + i * 32;
+            topk_w[static_cast<size_t>(m) * K + slot] = p[i] / ng;
+        }
+        base += __popc(bal);
+    }
+    if (lane < Ks) {
+        topk_idx[static_cast<size_t>(m) * K + Kg + lane] = Ng + lane;
+        topk_w[static_cast<size_t>(m) * K + Kg + lane] = ps / ks_sum;
+    }
+
+    if (s_MN != nullptr) {
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int j = lane + i * 32;
+            if (j < Ng) {
+                const bool sel = (picked >> i) & 1u;
+                s_MN[static_cast<size_t>(m) * N + j] = sel ? p[i] / ng : 0.0f;
+                s_postsoft_MN[static_cast<size_t>(m) * N + j] = sel ? p[i] : 0.0f;
+                if (sel) mask_NM[static_cast<size_t>(j) * M + m] = 1;
+            }
+        }
+        if (lane < Ks) {
+            s_MN[static_cast<size_t>(m) * N + Ng + lane] = ps / ks_sum;
+            s_postsoft_MN[static_cast<size_t>(m) * N + Ng + lane] = ps;
+            mask_NM[static_cast<size_t>(Ng + lane) * M + m] = 1;
+        }
+        if (lane == 0) {
+            Ng_M[m] = ng;
+            Ks_M[m] = ks_sum;
+        }
+    }
+}
+
+// Dense mask / weights of an external router -> compact [M,K] form (ascending expert id).
+__global__ void topk_from_mask_kernel(const int* __restrict__ mask, long long m_sn, long long m_sm,
+                                      const float* __restrict__ s, long long s_sn, long long s_sm, int M, int N, int K,
+                                      int* __restrict__ topk_idx, float* __restrict__ topk_w, int* status) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    int cnt = 0;
+    for (int e = 0; e < N; ++e) {
+        if (mask[e * m_sn + m * m_sm] != 0) {
+            if (cnt < K) {
+                topk_idx[static_cast<size_t>(m) * K + cnt] = e;
+                topk_w[static_cast<size_t>(m) * K + cnt] = s[e * s_sn + m * s_sm];
+            }
+            ++cnt;
+        }
+    }
+    if (cnt != K) {
+        atomicCAS(status, 0, DEV_BAD_TOPK_COUNT);
+        for (int k = cnt; k < K; ++k) {  // keep later kernels in bounds: route the missing slots to expert 0 with weight 0
+            topk_idx[static_cast<size_t>(m) * K + k] = 0;
+            topk_w[static_cast<size_t>(m) * K + k] = 0.0f;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ permutation
+// Pass A: per-chunk histogram.  counts[c*N + e] = tokens of chunk c routed to expert e.
+__global__ void perm_count_kernel(const int* __restrict__ topk_idx, int M, int N, int K, int* __restrict__ counts,
+                                  int* status) {
+    extern __shared__ int sh[];
+    const int warps = blockDim.x >> 5;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* hist = sh + w * N;
+    const int chunk = blockIdx.x * warps + w;
+    const int m0 = chunk * CHUNK_TOKENS;
+    if (m0 >= M) return;
+    for (int e = lane; e < N; e += 32) hist[e] = 0;
+    __syncwarp();
+    for (int t = lane; t < CHUNK_TOKENS; t += 32) {
+        const int m = m0 + t;
+        if (m < M) {
+            for (int k = 0; k < K; ++k) {
+                int e = topk_idx[static_cast<size_t>(m) * K + k];
+                if (e < 0 || e >= N) { atomicCAS(status, 0, DEV_BAD_EXPERT_ID); e = 0; }
+                atomicAdd(&hist[e], 1);
+            }
+        }
+    }
+    __syncwarp();
+    for (int e = lane; e < N; e += 32) counts[static_cast<size_t>(chunk) * N + e] = hist[e];
+}
+
+// Pass B (one block): per-expert exclusive scan over chunks (in place), then the expert-level tables.
+__global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, int N, int K, long long save_rows,
+                                 long long* __restrict__ sizes, int* __restrict__ cumsums, int* __restrict__ pad_off,
+                                 int* __restrict__ tile_expert, int* __restrict__ sched, int tile_capacity) {
+    __shared__ int s_cnt[MAX_EXPERTS];
+    __shared__ int s_cum[MAX_EXPERTS + 1];
+    __shared__ int s_pad[MAX_EXPERTS + 1];
+    __shared__ int s_saved;
+    const int e = threadIdx.x;
+    if (e == 0) s_saved = 0;
+    int total = 0;
+    if (e < N) {
+        for (int c = 0; c < n_chunks; ++c) {
+            const int v = counts[static_cast<size_t>(c) * N + e];
+            counts[static_cast<size_t>(c) * N + e] = total;
+            total += v;
+        }
+        s_cnt[e] = total;
+        sizes[e] = total;
+    }
+    __syncthreads();
+    if (e == 0) {  // N <= 1024: a serial scan costs about a microsecond
+        int c = 0, p = 0;
+        for (int i = 0; i < N; ++i) {
+            s_cum[i] = c;
+            s_pad[i] = p;
+            c += s_cnt[i];
+            p += (s_cnt[i] + TILE_M - 1) / TILE_M * TILE_M;
+        }
+        s_cum[N] = c;
+        s_pad[N] = p;
+    }
+    __syncthreads();
+    if (e < N) {
+        cumsums[e] = s_cum[e];
+        pad_off[e] = s_pad[e];
+        const int ntile = (s_pad[e + 1] - s_pad[e]) / TILE_M;
+        const int t0 = s_pad[e] / TILE_M;
+        for (int t = 0; t < ntile && t0 + t < tile_capacity; ++t) tile_expert[t0 + t] = e;
+        // tiles of this expert whose last row index (in the unpadded order) is below save_rows
+        long long fit = (save_rows - s_cum[e]) / TILE_M;
+        if (fit < 0) fit = 0;
+        if (fit > ntile) fit = ntile;
+        if (fit > 0) atomicAdd(&s_saved, static_cast<int>(fit));
+    }
+    __syncthreads();
+    if (e == 0) {
+        cumsums[N] = M * K;  // the reference stores the total here unconditionally
+        pad_off[N] = s_pad[N];
+        sched[SCHED_N_TILES] = s_pad[N] / TILE_M;
+        sched[SCHED_N_SAVED_TILES] = s_saved;
+        sched[SCHED_PAD_ROWS] = s_pad[N];
+        for (int i = 3; i < SCHED_WORDS; ++i) sched[i] = 0;
+    }
+}
+
+// Pass C: every (token, k) pair gets its row.  Inside an expert rows ascend with the token id: a warp walks its
+// chunk 32 tokens at a time and ranks the lanes that chose the same expert with a per-expert bit mask.
+__global__ void perm_fill_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
+                                 const int* __restrict__ chunk_off, const int* __restrict__ cumsums,
+                                 const int* __restrict__ pad_off, int M, int N, int K, int* __restrict__ idx,
+                                 int* __restrict__ which, int* __restrict__ row_token, float* __restrict__ row_weight,
+                                 int* __restrict__ pos) {
+    extern __shared__ int sh[];
+    const int warps = blockDim.x >> 5;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned* bits = reinterpret_cast<unsigned*>(sh) + w * 2 * N;
+    int* running = sh + w * 2 * N + N;
+    const int chunk = blockIdx.x * warps + w;
+    const int m0 = chunk * CHUNK_TOKENS;
+    if (m0 >= M) return;
+    for (int e = lane; e < N; e += 32) running[e] = chunk_off[static_cast<size_t>(chunk) * N + e];
+    for (int g0 = 0; g0 < CHUNK_TOKENS; g0 += 32) {
+        for (int e = lane; e < N; e += 32) bits[e] = 0u;
+        __syncwarp();
+        const int m = m0 + g0 + lane;
+        const bool live = m < M;
+        if (live)
+            for (int k = 0; k < K; ++k) {
+                int e = topk_idx[static_cast<size_t>(m) * K + k];
+                if (e < 0 || e >= N) e = 0;
+                atomicOr(&bits[e], 1u << lane);
+            }
+        __syncwarp();
+        if (live)
+            for (int k = 0; k < K; ++k) {
+                int e = topk_idx[static_cast<size_t>(m) * K + k];
+                if (e < 0 || e >= N) e = 0;
+                const int rank = running[e] + __popc(bits[e] & ((1u << lane) - 1u));
+                const int r = cumsums[e] + rank;
+                const int pr = pad_off[e] + rank;
+                idx[r] = m;
+                which[r] = k;
+                row_token[pr] = m;
+                row_weight[pr] = topk_w[static_cast<size_t>(m) * K + k];
+                pos[static_cast<size_t>(m) * K + k] = pr;
+            }
+        __syncwarp();
+        for (int e = lane; e < N; e += 32) running[e] += __popc(bits[e]);
+        __syncwarp();
+    }
+}
+
+// ------------------------------------------------------------------------------------------ row movement
+// dst[r,:] = src[row_token[r],:], zeros on padding rows.  One warp per row, 16 bytes per lane per step.
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ row_token,
+                                   const int* __restrict__ sched, int vec_per_row, uint4* __restrict__ dst) {
+    const int lane = threadIdx.x & 31;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    const int rows = sched[SCHED_PAD_ROWS];
+    for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps_total) {
+        const int tok = row_token[r];
+        uint4* d = dst + static_cast<size_t>(r) * vec_per_row;
+        if (tok >= 0) {
+            const uint4* s = src + static_cast<size_t>(tok) * vec_per_row;
+            for (int c = lane; c < vec_per_row; c += 32) d[c] = __ldg(s + c);
+        } else {
+            for (int c = lane; c < vec_per_row; c += 32) d[c] = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+__device__ __forceinline__ void acc_bf16x8(const uint4& q, float (&a)[8]) {
+    a[0] += __uint_as_float(q.x << 16); a[1] += __uint_as_float(q.x & 0xFFFF0000u);
+    a[2] += __uint_as_float(q.y << 16); a[3] += __uint_as_float(q.y & 0xFFFF0000u);
+    a[4] += __uint_as_float(q.z << 16); a[5] += __uint_as_float(q.z & 0xFFFF0000u);
+    a[6] += __uint_as_float(q.w << 16); a[7] += __uint_as_float(q.w & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+
+// dst[m,:] = bf16(sum_k src[pos[m,k],:]) with fp32 accumulation in ascending k: deterministic, no atomics.
+template <int KT>
+__global__ void combine_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ pos, int M, int K,
+                                    int vec_per_row, uint4* __restrict__ dst) {
+    const long long total = static_cast<long long>(M) * vec_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int m = static_cast<int>(i / vec_per_row);
+        const int c = static_cast<int>(i - static_cast<long long>(m) * vec_per_row);
+        float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (KT > 0) {
+            uint4 q[KT > 0 ? KT : 1];
+#pragma unroll
+            for (int k = 0; k < KT; ++k)
+                q[k] = __ldg(src + static_cast<size_t>(pos[static_cast<size_t>(m) * KT + k]) * vec_per_row + c);
+#pragma unroll
+            for (int k = 0; k < KT; ++k) acc_bf16x8(q[k], a);
+        } else {
+            for (int k = 0; k < K; ++k)
+                acc_bf16x8(__ldg(src + static_cast<size_t>(pos[static_cast<size_t>(m) * K + k]) * vec_per_row + c), a);
+        }
+        uint4 o;
+        o.x = pack2(a[0], a[1]); o.y = pack2(a[2], a[3]); o.z = pack2(a[4], a[5]); o.w = pack2(a[6], a[7]);
+        dst[i] = o;
+    }
+}
+
+// G_s[e, token] = sum of the row's partial sums (dense output pre-zeroed by the caller side of this file).
+__global__ void scatter_gs_kernel(const float* __restrict__ gs_part, int n_part, const int* __restrict__ row_token,
+                                  const int* __restrict__ tile_expert, const int* __restrict__ sched, int M,
+                                  float* __restrict__ G_s) {
+    const int rows = sched[SCHED_PAD_ROWS];
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+        const int tok = row_token[r];
+        if (tok < 0) continue;
+        float s = 0.0f;
+        for (int p = 0; p < n_part; ++p) s += gs_part[static_cast<size_t>(r) * n_part + p];
+        G_s[static_cast<size_t>(tile_expert[r / TILE_M]) * M + tok] = s;
+    }
+}
+
+// Router backward, one warp per token (momoe/topk_router.py:11-56 of the reference).
+__global__ void router_backward_kernel(const float* __restrict__ G_s, long long g_sn, long long g_sm,
+                                       const float* __restrict__ postsoft, const float* __restrict__ s_norm,
+                                       const float* __restrict__ Ng_M, const float* __restrict__ Ks_M,
+                                       const int* __restrict__ mask_NM, int M, int N, int Ks,
+                                       __nv_bfloat16* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (m >= M) return;
+    const int Ng = N - Ks;
+    const size_t ro = static_cast<size_t>(m) * N;
+    // group 0: gating experts [0, Ng) with the selection mask; group 1: shared experts [Ng, N)
+    for (int grp = 0; grp < 2; ++grp) {
+        const int lo = grp == 0 ? 0 : Ng;
+        const int hi = grp == 0 ? Ng : N;
+        if (hi == lo) continue;
+        float dot = 0.0f;
+        for (int j = lo + lane; j < hi; j += 32) {
+            const float gsv = G_s[j * g_sn + m * g_sm];
+            const float mk = grp == 0 ? static_cast<float>(mask_NM[static_cast<size_t>(j) * M + m]) : 1.0f;
+            dot += gsv * s_norm[ro + j] * mk;
+        }
+        dot = warp_sum(dot);
+        const float inv = 1.0f / (grp == 0 ? Ng_M[m] : Ks_M[m]);
+        float t = 0.0f;
+        for (int j = lo + lane; j < hi; j += 32) t += (G_s[j * g_sn + m * g_sm] - dot) * inv * postsoft[ro + j];
+        t = warp_sum(t);
+        for (int j = lo + lane; j < hi; j += 32) {
+            const float u = (G_s[j * g_sn + m * g_sm] - dot) * inv;
+            out[ro + j] = __float2bfloat16_rn(postsoft[ro + j] * (u - t));
+        }
+    }
+}
+
+static inline int cdiv(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace momoe
+
+using namespace momoe;
+
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? MOMOE_OK : MOMOE_ERR_CUDA)
+
+extern "C" __attribute__((visibility("default"))) int momoe_route_topk(const void* logits_MN, const float* biases_N, int32_t M, int32_t N, int32_t K,
+                                int32_t Ks, int32_t* topk_idx_MK, float* topk_w_MK, int32_t* mask_NM, float* s_MN,
+                                float* s_postsoft_MN, float* Ng_M, float* Ks_M, momoe_stream_t stream) {
+    if (logits_MN == nullptr || biases_N == nullptr || topk_idx_MK == nullptr || topk_w_MK == nullptr)
+        return MOMOE_ERR_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || Ks < 0 || Ks >= K || K - Ks > N - Ks) return MOMOE_ERR_ARG;
+    if (N > MAX_EXPERTS || K > MAX_TOPK || Ks > 32) return MOMOE_ERR_TOO_LARGE;
+    const bool dense = mask_NM != nullptr;
+    if (dense != (s_MN != nullptr) || dense != (s_postsoft_MN != nullptr) || dense != (Ng_M != nullptr) ||
+        dense != (Ks_M != nullptr))
+        return MOMOE_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dense) {
+        if (cudaMemsetAsync(mask_NM, 0, sizeof(int32_t) * static_cast<size_t>(N) * M, st) != cudaSuccess)
+            return MOMOE_ERR_CUDA;
+    }
+    const int Ng = N - Ks;
+    const int npl = (Ng + 31) / 32;
+    const int warps = 8;
+    const dim3 grid(cdiv(M, warps)), block(warps * 32);
+    const __nv_bfloat16* lg = static_cast<const __nv_bfloat16*>(logits_MN);
+#define ROUTE(NPL)                                                                                              \
+    route_topk_kernel<NPL><<<grid, block, 0, st>>>(lg, biases_N, M, N, K, Ks, topk_idx_MK, topk_w_MK, mask_NM, \
+                                                   s_MN, s_postsoft_MN, Ng_M, Ks_M)
+    if (npl <= 1) ROUTE(1);
+    else if (npl <= 2) ROUTE(2);
+    else if (npl <= 4) ROUTE(4);
+    else if (npl <= 8) ROUTE(8);
+    else if (npl <= 16) ROUTE(16);
+    else ROUTE(32);
+#undef ROUTE
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_topk_from_mask(const int32_t* mask_NM, int64_t mask_stride_n, int64_t mask_stride_m,
+                                    const float* s_NM, int64_t s_stride_n, int64_t s_stride_m, int32_t M, int32_t N,
+                                    int32_t K, int32_t* topk_idx_MK, float* topk_w_MK, int32_t* status,
+                                    momoe_stream_t stream) {
+    if (mask_NM == nullptr || s_NM == nullptr || topk_idx_MK == nullptr || topk_w_MK == nullptr || status == nullptr)
+        return MOMOE_ERR_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || K > N) return MOMOE_ERR_ARG;
+    if (N > MAX_EXPERTS || K > MAX_TOPK) return MOMOE_ERR_TOO_LARGE;
+    topk_from_mask_kernel<<<cdiv(M, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        mask_NM, mask_stride_n, mask_stride_m, s_NM, s_stride_n, s_stride_m, M, N, K, topk_idx_MK, topk_w_MK, status);
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) size_t momoe_permutation_workspace_bytes(int32_t M, int32_t N, int32_t K) {
+    (void)K;
+    if (M <= 0 || N <= 0) return 0;
+    const size_t chunks = (static_cast<size_t>(M) + CHUNK_TOKENS - 1) / CHUNK_TOKENS;
+    return chunks * N * sizeof(int32_t);
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N,
+                                       int32_t K, int64_t save_rows, int64_t* sizes_N, int32_t* cumsums_N1,
+                                       int32_t* idx_Msum, int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert,
+                                       int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
+                                       int64_t rows_capacity, void* workspace, size_t workspace_bytes, int32_t* status,
+                                       momoe_stream_t stream) {
+    if (topk_idx_MK == nullptr || topk_w_MK == nullptr || sizes_N == nullptr || cumsums_N1 == nullptr ||
+        idx_Msum == nullptr || which_Msum == nullptr || pad_off == nullptr || tile_expert == nullptr ||
+        sched == nullptr || row_token == nullptr || row_weight == nullptr || pos_MK == nullptr ||
+        workspace == nullptr || status == nullptr)
+        return MOMOE_ERR_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || K > N || save_rows < 0) return MOMOE_ERR_ARG;
+    if (N > MAX_EXPERTS || K > MAX_TOPK) return MOMOE_ERR_TOO_LARGE;
+    if (static_cast<int64_t>(M) * K > 0x7fffffffLL - static_cast<int64_t>(N) * TILE_M) return MOMOE_ERR_TOO_LARGE;
+    if (rows_capacity < momoe_sorted_rows_capacity(M, K, N)) return MOMOE_ERR_ARG;
+    if (workspace_bytes < momoe_permutation_workspace_bytes(M, N, K)) return MOMOE_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int* counts = static_cast<int*>(workspace);
+    const int n_chunks = cdiv(M, CHUNK_TOKENS);
+    const int warps = 4;
+    const int blocks = cdiv(n_chunks, warps);
+    // padding rows: token -1, weight 0
+    if (cudaMemsetAsync(row_token, 0xFF, sizeof(int32_t) * static_cast<size_t>(rows_capacity), st) != cudaSuccess ||
+        cudaMemsetAsync(row_weight, 0, sizeof(float) * static_cast<size_t>(rows_capacity), st) != cudaSuccess)
+        return MOMOE_ERR_CUDA;
+    perm_count_kernel<<<blocks, warps * 32, warps * N * sizeof(int), st>>>(topk_idx_MK, M, N, K, counts, status);
+    perm_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(counts, n_chunks, M, N, K, save_rows,
+                                                reinterpret_cast<long long*>(sizes_N), cumsums_N1, pad_off,
+                                                tile_expert, sched, static_cast<int>(momoe_tile_capacity(M, K, N)));
+    perm_fill_kernel<<<blocks, warps * 32, warps * 2 * N * sizeof(int), st>>>(
+        topk_idx_MK, topk_w_MK, counts, cumsums_N1, pad_off, M, N, K, idx_Msum, which_Msum, row_token, row_weight,
+        pos_MK);
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
+                                 momoe_stream_t stream) {
+    if (plan == nullptr || src == nullptr || dst_sorted == nullptr || plan->row_token == nullptr ||
+        plan->sched == nullptr)
+        return MOMOE_ERR_ARG;
+    if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
+    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_sorted)) & 15) != 0) return MOMOE_ERR_ARG;
+    const int blocks = sm_count() * 8;
+    gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), plan->row_token, plan->sched, cols / 8, static_cast<uint4*>(dst_sorted));
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_combine_rows(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
+                                  momoe_stream_t stream) {
+    if (plan == nullptr || src_sorted == nullptr || dst == nullptr || plan->pos_MK == nullptr) return MOMOE_ERR_ARG;
+    if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
+    if (((reinterpret_cast<uintptr_t>(src_sorted) | reinterpret_cast<uintptr_t>(dst)) & 15) != 0) return MOMOE_ERR_ARG;
+    const int vec = cols / 8;
+    const long long total = static_cast<long long>(plan->M) * vec;
+    int blocks = cdiv(total, 256);
+    const int cap = sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint4* s = static_cast<const uint4*>(src_sorted);
+    uint4* d = static_cast<uint4*>(dst);
+    switch (plan->K) {
+        case 2: combine_rows_kernel<2><<<blocks, 256, 0, st>>>(s, plan->pos_MK, plan->M, plan->K, vec, d); break;
+        case 4: combine_rows_kernel<4><<<blocks, 256, 0, st>>>(s, plan->pos_MK, plan->M, plan->K, vec, d); break;
+        case 6: combine_rows_kernel<6><<<blocks, 256, 0, st>>>(s, plan->pos_MK, plan->M, plan->K, vec, d); break;
+        case 8: combine_rows_kernel<8><<<blocks, 256, 0, st>>>(s, plan->pos_MK, plan->M, plan->K, vec, d); break;
+        default: combine_rows_kernel<0><<<blocks, 256, 0, st>>>(s, plan->pos_MK, plan->M, plan->K, vec, d); break;
+    }
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_scatter_gs(const momoe_plan_t* plan, const float* gs_part, int32_t n_part, float* G_s_NM,
+                                momoe_stream_t stream) {
+    if (plan == nullptr || gs_part == nullptr || G_s_NM == nullptr || n_part <= 0 || plan->row_token == nullptr ||
+        plan->tile_expert == nullptr)
+        return MOMOE_ERR_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(G_s_NM, 0, sizeof(float) * static_cast<size_t>(plan->N) * plan->M, st) != cudaSuccess)
+        return MOMOE_ERR_CUDA;
+    scatter_gs_kernel<<<sm_count() * 4, 256, 0, st>>>(gs_part, n_part, plan->row_token, plan->tile_expert, plan->sched,
+                                                      plan->M, G_s_NM);
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_router_backward(const float* G_s, int64_t gs_stride_n, int64_t gs_stride_m,
+                                     const float* s_postsoft_MN, const float* s_MN, const float* Ng_M,
+                                     const float* Ks_M, const int32_t* mask_NM, int32_t M, int32_t N, int32_t Ks,
+                                     void* G_logits_MN, momoe_stream_t stream) {
+    if (G_s == nullptr || s_postsoft_MN == nullptr || s_MN == nullptr || Ng_M == nullptr || Ks_M == nullptr ||
+        mask_NM == nullptr || G_logits_MN == nullptr)
+        return MOMOE_ERR_ARG;
+    if (M <= 0 || N <= 0 || Ks < 0 || Ks >= N) return MOMOE_ERR_ARG;
+    const int warps = 8;
+    router_backward_kernel<<<cdiv(M, warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        G_s, gs_stride_n, gs_stride_m, s_postsoft_MN, s_MN, Ng_M, Ks_M, mask_NM, M, N, Ks,
+        static_cast<__nv_bfloat16*>(G_logits_MN));
+    return LAUNCH_OK();
+}

@@ -1,0 +1,213 @@
+"""Host-side plumbing above the C ABI: device buffers (torch), the routing plan, and the forward / backward
+sequences of kernel launches.  No arithmetic on tensor contents happens here."""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import lib, ptr, stream_ptr, check
+
+TILE_M = 128
+_status_words = {}
+
+
+def status_word(device):
+    """Per-device int32 word the kernels report device-side problems into (0 = fine)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status_words[key]
+
+
+_STATUS_TEXT = {101: "TMA producer wait timed out", 102: "MMA issuer wait timed out",
+                103: "epilogue wait timed out", 201: "a token does not have exactly K experts in mask_NM",
+                202: "expert id out of range"}
+
+
+def check_status(device=None):
+    """Synchronises and raises if any kernel recorded a device-side problem.  Clears the word."""
+    w = status_word(device if device is not None else torch.cuda.current_device())
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise RuntimeError("momoe device status %d: %s" % (v, _STATUS_TEXT.get(v, "unknown")))
+
+
+def save_rows(Msum, save_percent):
+    return int(Msum * save_percent / 100.0)
+
+
+class RoutingPlan:
+    """Device tables of one routing decision (see momoe_plan_t) plus the reference-visible permutation."""
+
+    def __init__(self, M, N, K, D, H, device, save_percent=0.0):
+        self.M, self.N, self.K, self.D, self.H = M, N, K, D, H
+        self.device = device
+        self.Msum = M * K
+        self.save_rows = save_rows(self.Msum, save_percent)
+        self.rows_capacity = int(lib.momoe_sorted_rows_capacity(M, K, N))
+        self.tile_capacity = int(lib.momoe_tile_capacity(M, K, N))
+        self.saved_tile_capacity = min(self.tile_capacity, self.save_rows // TILE_M + N) if self.save_rows > 0 else 0
+        self.recomp_tile_capacity = min(self.tile_capacity, (self.Msum - self.save_rows) // TILE_M + N + 1)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.sizes = torch.empty(N, dtype=torch.int64, device=device)
+        self.cumsums = torch.empty(N + 1, **i32)
+        self.idx = torch.empty(self.Msum, **i32)
+        self.which = torch.empty(self.Msum, **i32)
+        self.pad_off = torch.empty(N + 1, **i32)
+        self.tile_expert = torch.empty(self.tile_capacity, **i32)
+        self.sched = torch.empty(8, **i32)
+        self.row_token = torch.empty(self.rows_capacity, **i32)
+        self.row_weight = torch.empty(self.rows_capacity, dtype=torch.float32, device=device)
+        self.pos = torch.empty(self.Msum, **i32)
+        self.status = status_word(device)
+        self.topk_idx = None
+        self.topk_w = None
+        self.c = _lib.Plan(M=M, N=N, K=K, D=D, H=H, reserved=0, rows_capacity=self.rows_capacity,
+                           sched=self.sched.data_ptr(), tile_expert=self.tile_expert.data_ptr(),
+                           pad_off=self.pad_off.data_ptr(), row_token=self.row_token.data_ptr(),
+                           row_weight=self.row_weight.data_ptr(), pos_MK=self.pos.data_ptr(),
+                           status=self.status.data_ptr())
+
+    @property
+    def ref(self):
+        return C.byref(self.c)
+
+    def build(self, topk_idx, topk_w):
+        self.topk_idx, self.topk_w = topk_idx, topk_w
+        nbytes = int(lib.momoe_permutation_workspace_bytes(self.M, self.N, self.K))
+        ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=self.device)
+        check(lib.momoe_build_permutation(ptr(topk_idx), ptr(topk_w), self.M, self.N, self.K, self.save_rows,
+                                          ptr(self.sizes), ptr(self.cumsums), ptr(self.idx), ptr(self.which),
+                                          ptr(self.pad_off), ptr(self.tile_expert), ptr(self.sched),
+                                          ptr(self.row_token), ptr(self.row_weight), ptr(self.pos),
+                                          self.rows_capacity, ptr(ws), nbytes, ptr(self.status), stream_ptr()),
+              "momoe_build_permutation")
+        return self
+
+    @classmethod
+    def from_topk(cls, topk_idx, topk_w, N, D, H, save_percent=0.0):
+        M, K = topk_idx.shape
+        return cls(M, N, K, D, H, topk_idx.device, save_percent).build(topk_idx, topk_w)
+
+    @classmethod
+    def from_mask(cls, mask_NM, s_NM, K, D, H, save_percent=0.0):
+        """Compact an external router's dense mask_NM (int32, any strides) and s_NM (fp32, any strides)."""
+        N, M = mask_NM.shape
+        if mask_NM.dtype != torch.int32:
+            mask_NM = mask_NM.to(torch.int32)
+        if s_NM.dtype != torch.float32:
+            s_NM = s_NM.to(torch.float32)
+        dev = mask_NM.device
+        plan = cls(M, N, K, D, H, dev, save_percent)
+        topk_idx = torch.empty((M, K), dtype=torch.int32, device=dev)
+        topk_w = torch.empty((M, K), dtype=torch.float32, device=dev)
+        check(lib.momoe_topk_from_mask(ptr(mask_NM), mask_NM.stride(0), mask_NM.stride(1), ptr(s_NM),
+                                       s_NM.stride(0), s_NM.stride(1), M, N, K, ptr(topk_idx), ptr(topk_w),
+                                       ptr(plan.status), stream_ptr()), "momoe_topk_from_mask")
+        return plan.build(topk_idx, topk_w)
+
+
+def route_topk(logits_MN, biases_N, K, Ks, dense=True):
+    """Router after the gate GEMM.  Returns (topk_idx, topk_w, dense dict or None)."""
+    _lib.require_cuda(logits_MN, biases_N)
+    M, N = logits_MN.shape
+    dev = logits_MN.device
+    logits_MN = logits_MN.contiguous()
+    biases_N = biases_N.to(device=dev, dtype=torch.float32).contiguous()
+    topk_idx = torch.empty((M, K), dtype=torch.int32, device=dev)
+    topk_w = torch.empty((M, K), dtype=torch.float32, device=dev)
+    d = None
+    if dense:
+        d = dict(mask_NM=torch.empty((N, M), dtype=torch.int32, device=dev),
+                 s_MN=torch.empty((M, N), dtype=torch.float32, device=dev),
+                 s_postsoft_MN=torch.empty((M, N), dtype=torch.float32, device=dev),
+                 Ng_M=torch.empty(M, dtype=torch.float32, device=dev),
+                 Ks_M=torch.empty(M, dtype=torch.float32, device=dev))
+    check(lib.momoe_route_topk(ptr(logits_MN), ptr(biases_N), M, N, K, Ks, ptr(topk_idx), ptr(topk_w),
+                               ptr(d["mask_NM"]) if d else None, ptr(d["s_MN"]) if d else None,
+                               ptr(d["s_postsoft_MN"]) if d else None, ptr(d["Ng_M"]) if d else None,
+                               ptr(d["Ks_M"]) if d else None, stream_ptr()), "momoe_route_topk")
+    return topk_idx, topk_w, d
+
+
+def gather_rows(plan, src, cols):
+    dst = torch.empty((plan.rows_capacity, cols), dtype=torch.bfloat16, device=src.device)
+    check(lib.momoe_gather_rows(plan.ref, ptr(src), cols, ptr(dst), stream_ptr()), "momoe_gather_rows")
+    return dst
+
+
+def combine_rows(plan, src_sorted, cols):
+    dst = torch.empty((plan.M, cols), dtype=torch.bfloat16, device=src_sorted.device)
+    check(lib.momoe_combine_rows(plan.ref, ptr(src_sorted), cols, ptr(dst), stream_ptr()), "momoe_combine_rows")
+    return dst
+
+
+def experts_forward(plan, x_MD, W1, W2):
+    """x_MD bf16 [M,D] contiguous; W1 bf16 [N,D,2H], W2 bf16 [N,H,D] contiguous.
+    Returns y_MD bf16 and the (a, b) buffers saved for the backward pass (None when nothing is saved)."""
+    dev = x_MD.device
+    D, H = plan.D, plan.H
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    x_sorted = gather_rows(plan, x_MD, D)
+    h = torch.empty((plan.rows_capacity, H), **bf)
+    a_save = b_save = None
+    mode = 0
+    if plan.saved_tile_capacity > 0:
+        a_save = torch.empty((plan.saved_tile_capacity * TILE_M, H), **bf)
+        b_save = torch.empty((plan.saved_tile_capacity * TILE_M, H), **bf)
+        mode = 1
+    check(lib.momoe_up_swiglu(plan.ref, ptr(x_sorted), ptr(W1), ptr(h), ptr(a_save), ptr(b_save), mode,
+                              stream_ptr()), "momoe_up_swiglu")
+    del x_sorted
+    y_sorted = torch.empty((plan.rows_capacity, D), **bf)
+    check(lib.momoe_down_scale(plan.ref, ptr(h), ptr(W2), ptr(y_sorted), stream_ptr()), "momoe_down_scale")
+    y = combine_rows(plan, y_sorted, D)
+    return y, a_save, b_save
+
+
+def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=True):
+    """Returns G_x bf16 [M,D], G_W1 bf16, G_W2 bf16, G_s (dense fp32 [N,M] or per-row partial sums)."""
+    dev = x_MD.device
+    D, H, N = plan.D, plan.H, plan.N
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    g_sorted = gather_rows(plan, g_MD, D)
+    x_sorted = gather_rows(plan, x_MD, D)
+    a_rec = b_rec = None
+    if plan.recomp_tile_capacity > 0:
+        a_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
+        b_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
+        check(lib.momoe_up_swiglu(plan.ref, ptr(x_sorted), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2, stream_ptr()),
+              "momoe_up_swiglu (recompute)")
+    n_part = (H + 127) // 128
+    gz = torch.empty((plan.rows_capacity, 2 * H), **bf)
+    hs = torch.empty((plan.rows_capacity, H), **bf)
+    gs_part = torch.empty((plan.rows_capacity, n_part), dtype=torch.float32, device=dev)
+    check(lib.momoe_dgrad2_swiglu_bwd(plan.ref, ptr(g_sorted), ptr(W2), ptr(a_save), ptr(b_save), ptr(a_rec),
+                                      ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), stream_ptr()),
+          "momoe_dgrad2_swiglu_bwd")
+    del a_rec, b_rec
+    G_W2 = torch.empty_like(W2)
+    check(lib.momoe_wgrad(plan.ref, ptr(hs), H, ptr(g_sorted), D, ptr(G_W2), stream_ptr()), "momoe_wgrad (W2)")
+    G_W1 = torch.empty_like(W1)
+    check(lib.momoe_wgrad(plan.ref, ptr(x_sorted), D, ptr(gz), 2 * H, ptr(G_W1), stream_ptr()), "momoe_wgrad (W1)")
+    gx_sorted = g_sorted  # the gathered upstream gradient is dead after the W2 gradient; reuse its buffer
+    check(lib.momoe_dgrad1(plan.ref, ptr(gz), ptr(W1), ptr(gx_sorted), stream_ptr()), "momoe_dgrad1")
+    G_x = combine_rows(plan, gx_sorted, D)
+    if need_gs_dense:
+        G_s = torch.empty((N, plan.M), dtype=torch.float32, device=dev)
+        check(lib.momoe_scatter_gs(plan.ref, ptr(gs_part), n_part, ptr(G_s), stream_ptr()), "momoe_scatter_gs")
+    else:
+        G_s = gs_part
+    return G_x, G_W1, G_W2, G_s
+
+
+def router_backward(G_s_NM, s_postsoft_MN, s_MN, Ng_M, Ks_M, mask_NM, Ks):
+    N, M = G_s_NM.shape
+    if G_s_NM.dtype != torch.float32:
+        G_s_NM = G_s_NM.to(torch.float32)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=G_s_NM.device)
+    check(lib.momoe_router_backward(ptr(G_s_NM), G_s_NM.stride(0), G_s_NM.stride(1), ptr(s_postsoft_MN), ptr(s_MN),
+                                    ptr(Ng_M), ptr(Ks_M), ptr(mask_NM), M, N, Ks, ptr(out), stream_ptr()),
+          "momoe_router_backward")
+    return out

@@ -46,8 +46,11 @@ def gate_logits(x_MD: torch.Tensor, Wg_DN: torch.Tensor) -> torch.Tensor:
     return (x_MD.to(bf16).to(f32) @ Wg_DN.to(bf16).to(f32)).to(bf16)
 
 
-def router_from_logits(logits_MN: torch.Tensor, biases_N: torch.Tensor, K: int, Ks: int):
+def router_from_logits(logits_MN: torch.Tensor, biases_N: torch.Tensor, K: int, Ks: int, torch_topk: bool = False):
     """Everything in momoe/topk_router.py:96-120 after the gate GEMM.
+
+    Runs on the device of `logits_MN`.  With `torch_topk=True` the selection is `torch.topk` itself, i.e. on a
+    CUDA tensor exactly the call the reference makes; otherwise the documented tie rule is applied explicitly.
 
     logits_MN: bf16 [M, N].  biases_N: fp32 [N] (entries of shared experts are ignored).
     Returns dict with
@@ -58,16 +61,20 @@ def router_from_logits(logits_MN: torch.Tensor, biases_N: torch.Tensor, K: int, 
       topk_idx int32 [M, K] ascending expert ids of the selected + shared experts
     """
     M, N = logits_MN.shape
+    dev = logits_MN.device
     Ng = N - Ks
-    Lg = logits_MN[:, :Ng].to(f32)
-    p_g = torch.softmax(Lg, dim=-1)
-    s_MN = torch.empty((M, N), dtype=f32)
+    p_g = torch.softmax(logits_MN[:, :Ng], dim=-1, dtype=f32)
+    s_MN = torch.empty((M, N), dtype=f32, device=dev)
     if Ks > 0:
-        p_s = torch.softmax(logits_MN[:, Ng:].to(f32), dim=-1)
+        p_s = torch.softmax(logits_MN[:, Ng:], dim=-1, dtype=f32)
     else:
-        p_s = torch.empty((M, 0), dtype=f32)
-    sel = topk_lowest_index_first(p_g + biases_N[:Ng].to(f32)[None, :], K - Ks)
-    mask_MNg = torch.zeros((M, Ng), dtype=torch.bool)
+        p_s = torch.empty((M, 0), dtype=f32, device=dev)
+    score = p_g + biases_N.to(dev)[:Ng].to(f32)[None, :]
+    if torch_topk:
+        sel = torch.sort(torch.topk(score, K - Ks, dim=-1).indices, dim=-1).values
+    else:
+        sel = topk_lowest_index_first(score, K - Ks)
+    mask_MNg = torch.zeros((M, Ng), dtype=torch.bool, device=dev)
     mask_MNg.scatter_(1, sel, True)
     q = p_g * mask_MNg
     Ng_M = q.sum(dim=-1)
@@ -75,9 +82,9 @@ def router_from_logits(logits_MN: torch.Tensor, biases_N: torch.Tensor, K: int, 
     s_postsoft = torch.cat([q, p_s], dim=-1)
     s_MN[:, :Ng] = q / Ng_M[:, None]
     s_MN[:, Ng:] = p_s / Ks_M[:, None]
-    mask_NM = torch.ones((N, M), dtype=torch.int32)
+    mask_NM = torch.ones((N, M), dtype=torch.int32, device=dev)
     mask_NM[:Ng] = mask_MNg.T.to(torch.int32)
-    shared = torch.arange(Ng, N, dtype=sel.dtype)[None, :].expand(M, Ks)
+    shared = torch.arange(Ng, N, dtype=sel.dtype, device=dev)[None, :].expand(M, Ks)
     topk_idx = torch.cat([sel, shared], dim=-1).to(torch.int32)
     return dict(mask_NM=mask_NM.contiguous(), s_MN=s_MN, s_postsoft_MN=s_postsoft, Ng_M=Ng_M, Ks_M=Ks_M,
                 topk_idx=topk_idx)

@@ -45,3 +45,36 @@ def max_rel(a, b):
     a = a.double()
     b = b.double()
     return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU-side helpers
+# ---------------------------------------------------------------------------------------------------------
+def make_routing(M, N, K, seed, skew=0.0, device="cuda"):
+    """Seeded random routing: topk_idx int32 [M,K] ascending, topk_w fp32 [M,K] summing to 1 per token."""
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(M, N, generator=g) + skew * torch.randn(N, generator=g)[None, :]
+    idx = torch.sort(torch.topk(logits, K, dim=-1).indices, dim=-1).values.to(torch.int32)
+    w = torch.softmax(torch.gather(logits, 1, idx.long()), dim=-1).float()
+    return idx.to(device), w.to(device)
+
+
+def dense_from_topk(topk_idx, topk_w, N):
+    M, K = topk_idx.shape
+    mask = torch.zeros((M, N), dtype=torch.int32, device=topk_idx.device)
+    mask.scatter_(1, topk_idx.long(), 1)
+    s = torch.zeros((M, N), dtype=torch.float32, device=topk_idx.device)
+    s.scatter_(1, topk_idx.long(), topk_w)
+    return mask.T.contiguous(), s.T   # s_NM as a transposed view, like the reference router returns it
+
+
+def expert_rows(plan):
+    """Host copies of the plan tables: list of (expert, first padded row, count, token ids, weights)."""
+    cum = plan.cumsums.cpu().numpy()
+    pad = plan.pad_off.cpu().numpy()
+    idx = plan.idx.cpu()
+    out = []
+    for e in range(plan.N):
+        c = int(cum[e + 1] - cum[e])
+        out.append((e, int(pad[e]), c, idx[int(cum[e]):int(cum[e + 1])].long()))
+    return out

@@ -1,0 +1,175 @@
+"""GPU parity of the five grouped GEMM entry points against fp32 torch matmuls on the same bf16 inputs.
+Tolerance: one bf16 rounding of the output (relative 2^-8) plus fp32 accumulation-order noise."""
+import pytest
+import torch
+
+from helpers import cos, make_routing, max_rel
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import __graft_entry__
+    __graft_entry__.build()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    from momoe import ops
+    return ops
+
+
+def lib_of(ops):
+    from momoe import _lib
+    return _lib
+
+
+# M, N, K, D, H, skew
+SHAPES = [
+    (256, 4, 2, 128, 128, 0.0),
+    (512, 8, 2, 256, 128, 0.0),        # the reference's CPU-runnable configuration shape
+    (2048, 16, 4, 512, 384, 2.0),      # skewed, H not a multiple of 128
+    (300, 32, 6, 2176, 1152, 0.0),     # chart shape D2176 H1152; some experts may be empty
+    (96, 6, 3, 64, 32, 0.0),           # tiles smaller than one MMA tile in every dimension
+    (1024, 8, 8, 192, 136, 0.0),       # K == N (every expert sees every token); H % 64 != 0
+]
+
+
+def _setup(ops, M, N, K, D, H, skew, save_percent=0):
+    topk_idx, topk_w = make_routing(M, N, K, seed=M + D, skew=skew)
+    plan = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, H, save_percent)
+    g = torch.Generator().manual_seed(D + H)
+    x = torch.randn(M, D, generator=g).bfloat16().cuda()
+    W1 = (torch.randn(N, D, 2 * H, generator=g) * 0.05).bfloat16().cuda()
+    W2 = (torch.randn(N, H, D, generator=g) * 0.05).bfloat16().cuda()
+    torch.cuda.synchronize()
+    pad = plan.pad_off.cpu().tolist()
+    return plan, x, W1, W2, pad
+
+
+def _close(got, ref, what):
+    assert torch.isfinite(got.float()).all(), what + ": non-finite"
+    assert max_rel(got.float(), ref) < 8e-3, "%s: max-rel %g" % (what, max_rel(got.float(), ref))
+    assert cos(got.float(), ref) > 0.99995, what
+
+
+@pytest.mark.parametrize("M,N,K,D,H,skew", SHAPES)
+def test_up_swiglu_and_down_scale(ops, M, N, K, D, H, skew):
+    _lib = lib_of(ops)
+    plan, x, W1, W2, pad = _setup(ops, M, N, K, D, H, skew)
+    xs = ops.gather_rows(plan, x, D)
+    rows = pad[-1]
+    h = torch.full((plan.rows_capacity, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.lib.momoe_up_swiglu(plan.ref, _lib.ptr(xs), _lib.ptr(W1), _lib.ptr(h), None, None, 0,
+                                        _lib.stream_ptr()), "up")
+    ys = torch.full((plan.rows_capacity, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.lib.momoe_down_scale(plan.ref, _lib.ptr(h), _lib.ptr(W2), _lib.ptr(ys), _lib.stream_ptr()),
+               "down")
+    torch.cuda.synchronize()
+    ops.check_status()
+    h_ref = torch.zeros(rows, H, device="cuda")
+    y_ref = torch.zeros(rows, D, device="cuda")
+    for e in range(N):
+        lo, hi = pad[e], pad[e + 1]
+        if hi == lo:
+            continue
+        z = xs[lo:hi].float() @ W1[e].float()
+        a, b = z[:, :H], z[:, H:]
+        h_ref[lo:hi] = b * torch.sigmoid(b) * a
+        y_ref[lo:hi] = (h[lo:hi].float() @ W2[e].float()) * plan.row_weight[lo:hi, None]
+    _close(h[:rows], h_ref, "h")
+    _close(ys[:rows], y_ref, "y_sorted")
+    # padding rows are exact zeros
+    pad_rows = plan.row_token[:rows] < 0
+    assert float(h[:rows][pad_rows].float().abs().sum()) == 0.0
+    assert float(ys[:rows][pad_rows].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K,D,H,skew", SHAPES)
+@pytest.mark.parametrize("save_percent", [0, 50, 100])
+def test_backward_gemms(ops, M, N, K, D, H, skew, save_percent):
+    _lib = lib_of(ops)
+    L = _lib.lib
+    ptr, st = _lib.ptr, _lib.stream_ptr
+    plan, x, W1, W2, pad = _setup(ops, M, N, K, D, H, skew, save_percent)
+    rows = pad[-1]
+    bf = dict(dtype=torch.bfloat16, device="cuda")
+    xs = ops.gather_rows(plan, x, D)
+    gsort = ops.gather_rows(plan, torch.randn(M, D, generator=torch.Generator().manual_seed(9)).bfloat16().cuda(), D)
+    # forward with saving, then recomputation of the unsaved tiles
+    h = torch.empty((plan.rows_capacity, H), **bf)
+    a_s = b_s = None
+    if plan.saved_tile_capacity > 0:
+        a_s = torch.full((plan.saved_tile_capacity * 128, H), float("nan"), **bf)
+        b_s = torch.full((plan.saved_tile_capacity * 128, H), float("nan"), **bf)
+    _lib.check(L.momoe_up_swiglu(plan.ref, ptr(xs), ptr(W1), ptr(h), ptr(a_s), ptr(b_s), 1 if a_s is not None else 0,
+                                 st()), "up save")
+    a_r = torch.full((plan.recomp_tile_capacity * 128, H), float("nan"), **bf)
+    b_r = torch.full((plan.recomp_tile_capacity * 128, H), float("nan"), **bf)
+    _lib.check(L.momoe_up_swiglu(plan.ref, ptr(xs), ptr(W1), None, ptr(a_r), ptr(b_r), 2, st()), "up recompute")
+    n_part = (H + 127) // 128
+    gz = torch.full((plan.rows_capacity, 2 * H), float("nan"), **bf)
+    hs = torch.full((plan.rows_capacity, H), float("nan"), **bf)
+    gsp = torch.full((plan.rows_capacity, n_part), float("nan"), dtype=torch.float32, device="cuda")
+    _lib.check(L.momoe_dgrad2_swiglu_bwd(plan.ref, ptr(gsort), ptr(W2), ptr(a_s), ptr(b_s), ptr(a_r), ptr(b_r),
+                                         ptr(gz), ptr(hs), ptr(gsp), st()), "dgrad2")
+    dW2 = torch.full_like(W2, float("nan"))
+    dW1 = torch.full_like(W1, float("nan"))
+    _lib.check(L.momoe_wgrad(plan.ref, ptr(hs), H, ptr(gsort), D, ptr(dW2), st()), "wgrad2")
+    _lib.check(L.momoe_wgrad(plan.ref, ptr(xs), D, ptr(gz), 2 * H, ptr(dW1), st()), "wgrad1")
+    gx = torch.full((plan.rows_capacity, D), float("nan"), **bf)
+    _lib.check(L.momoe_dgrad1(plan.ref, ptr(gz), ptr(W1), ptr(gx), st()), "dgrad1")
+    torch.cuda.synchronize()
+    ops.check_status()
+
+    n_saved = int(plan.sched[1])
+    n_tiles = int(plan.sched[0])
+    assert 0 <= n_saved <= n_tiles
+    if save_percent == 0:
+        assert n_saved == 0
+    w = plan.row_weight[:rows, None]
+    gz_ref = torch.zeros(rows, 2 * H, device="cuda")
+    hs_ref = torch.zeros(rows, H, device="cuda")
+    gs_ref = torch.zeros(rows, device="cuda")
+    gx_ref = torch.zeros(rows, D, device="cuda")
+    dW1_ref = torch.zeros(N, D, 2 * H, device="cuda")
+    dW2_ref = torch.zeros(N, H, D, device="cuda")
+    a_all = torch.zeros(rows, H, device="cuda")
+    b_all = torch.zeros(rows, H, device="cuda")
+    for e in range(N):
+        lo, hi = pad[e], pad[e + 1]
+        if hi == lo:
+            continue
+        z = xs[lo:hi].float() @ W1[e].float()
+        a_all[lo:hi], b_all[lo:hi] = z[:, :H], z[:, H:]
+    # the kernels see bf16-rounded a, b (saved or recomputed into bf16 scratch)
+    a_q, b_q = a_all.bfloat16().float(), b_all.bfloat16().float()
+    if n_saved > 0:
+        _close(a_s[:n_saved * 128], a_all[:n_saved * 128], "a_saved")
+        _close(b_s[:n_saved * 128], b_all[:n_saved * 128], "b_saved")
+    if n_tiles > n_saved:
+        _close(a_r[:(n_tiles - n_saved) * 128], a_all[n_saved * 128:rows], "a_recomputed")
+        _close(b_r[:(n_tiles - n_saved) * 128], b_all[n_saved * 128:rows], "b_recomputed")
+    sig = torch.sigmoid(b_q)
+    hh = (a_q * b_q * sig).bfloat16().float()
+    for e in range(N):
+        lo, hi = pad[e], pad[e + 1]
+        if hi == lo:
+            continue
+        gh_raw = gsort[lo:hi].float() @ W2[e].float().T
+        gs_ref[lo:hi] = (gh_raw * hh[lo:hi]).sum(-1)
+        gh = gh_raw * w[lo:hi]
+        gz_ref[lo:hi, :H] = gh * b_q[lo:hi] * sig[lo:hi]
+        gz_ref[lo:hi, H:] = gh * a_q[lo:hi] * sig[lo:hi] * (1 + b_q[lo:hi] * (1 - sig[lo:hi]))
+        hs_ref[lo:hi] = hh[lo:hi] * w[lo:hi]
+        dW2_ref[e] = hs[lo:hi].float().T @ gsort[lo:hi].float()
+        dW1_ref[e] = xs[lo:hi].float().T @ gz[lo:hi].float()
+        gx_ref[lo:hi] = gz[lo:hi].float() @ W1[e].float().T
+    _close(gz[:rows], gz_ref, "gz")
+    _close(hs[:rows], hs_ref, "hs")
+    _close(gsp[:rows].sum(-1), gs_ref, "gs")
+    _close(gx[:rows], gx_ref, "gx_sorted")
+    _close(dW2, dW2_ref, "dW2")
+    _close(dW1, dW1_ref, "dW1")
+    sizes = plan.sizes.cpu()
+    for e in range(N):
+        if sizes[e] == 0:   # experts without tokens get exact zeros
+            assert float(dW1[e].float().abs().sum()) == 0.0 and float(dW2[e].float().abs().sum()) == 0.0
