@@ -1,0 +1,315 @@
+"""Benchmark of the MoMoE layer hot path: forward + backward tokens/s on the headline layer
+(D=2048, H=1024, N=128 experts, K=8 per token, bf16, 16384 tokens per GPU; synthetic seeded inputs).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--save-percent P] [--impl reference]
+
+Prints ONE JSON line.  `value` is measured with inputs resident in HBM; `e2e` runs the same step through the
+public `MoE` module starting from pinned host memory and reading the loss back every step.  `roofline` describes
+the grouped GEMM launch that takes the largest share of the step, timed with CUDA events inside the timed
+region.  `cpu_baseline` (rank 0, 1 GPU only) and `--impl reference` time the CPU restatement of the reference
+layer on the host cores on a bounded sample of the same layer.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "momoe-impl_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+METRIC = "MoE layer fwd+bwd tokens/sec (D2048 H1024 N128 K8 bf16)"
+CFG = dict(D=2048, H=1024, N=128, K=8, Ks=0, B=8, S=2048)
+CPU_SAMPLE_TOKENS = 2048
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops=float(p.get("bf16_tflops_sustained", p.get("bf16_tflops"))), hbm=float(p["hbm_gbs"]),
+                    source="measured (MEASURED_PEAKS.json, sustained bf16)")
+    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs (read-only queries)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+                power.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s, p in zip(sm, power) if p > 0.5 * max(power)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+def make_weights(seed, N, D, H, device, n_total, std=0.02):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    Wg = (torch.randn(D, n_total, generator=g) * std).bfloat16()
+    # expert weights are generated on the device to avoid shipping gigabytes through the host
+    gd = torch.Generator(device=device).manual_seed(seed + 1)
+    W1 = (torch.randn(N, D, 2 * H, generator=gd, device=device) * std).bfloat16()
+    W2 = (torch.randn(N, H, D, generator=gd, device=device) * std).bfloat16()
+    return Wg.to(device), W1, W2
+
+
+def cpu_sample(steps, warmup, seed=0):
+    """CPU restatement of the same layer on a bounded sample (CPU_SAMPLE_TOKENS tokens per step)."""
+    from oracle import momoe_oracle as orc
+    c = CFG
+    torch.manual_seed(seed)
+    torch.set_num_threads(os.cpu_count() or 1)
+    Wg = (torch.randn(c["D"], c["N"]) * 0.02).bfloat16()
+    W1 = (torch.randn(c["N"], c["D"], 2 * c["H"]) * 0.02).bfloat16()
+    W2 = (torch.randn(c["N"], c["H"], c["D"]) * 0.02).bfloat16()
+    state = orc.cpu_baseline_prepare(Wg, W1, W2)
+    del W1, W2
+    x = torch.randn(1, CPU_SAMPLE_TOKENS, c["D"])
+    biases = torch.zeros(c["N"])
+    for _ in range(warmup):
+        orc.cpu_baseline_step(state, x, biases, c["K"], c["Ks"])
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        orc.cpu_baseline_step(state, x, biases, c["K"], c["Ks"])
+    dt = (time.perf_counter() - t0) / steps
+    return dict(value=CPU_SAMPLE_TOKENS / dt, unit="tokens/s", cores=torch.get_num_threads(), kind="port",
+                sample="%d tokens per step of the same layer (D%d H%d N%d K%d), fp32 torch on host cores, %d steps"
+                       % (CPU_SAMPLE_TOKENS, c["D"], c["H"], c["N"], c["K"], steps),
+                ms_per_step=dt * 1e3)
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    cb = cpu_sample(args.steps, max(1, min(args.warmup, 3)))
+    line = dict(metric=METRIC, value=cb["value"], unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=cb["ms_per_step"], higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=dict(workload="cfg2 headline layer D2048 H1024 N128 K8, bounded CPU sample",
+                            tokens_per_step=CPU_SAMPLE_TOKENS, save_percent=0),
+                cpu_baseline={k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                e2e=dict(value=cb["value"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--save-percent", type=float, default=0.0)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory leg (profiling runs)")
+    ap.add_argument("--experts", type=int, default=CFG["N"], help="reduced case for profiler captures")
+    ap.add_argument("--tokens", type=int, default=CFG["B"] * CFG["S"], help="reduced case for profiler captures")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch.distributed as dist
+    import __graft_entry__
+    if rank == 0:
+        __graft_entry__.build()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+    import momoe
+    from momoe import ops
+
+    c = dict(CFG)
+    reduced = args.experts != c["N"] or args.tokens != c["B"] * c["S"]
+    if reduced:
+        c.update(N=args.experts, B=1, S=args.tokens)
+    D, H, N, K, Ks = c["D"], c["H"], c["N"], c["K"], c["Ks"]
+    M = c["B"] * c["S"]
+    if world > 1:
+        from momoe import ep
+        Wg, W1, W2 = make_weights(1234, N // world, D, H, dev, N)          # this rank's expert block
+        moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=args.save_percent, Wg_DN=Wg, Wl1_ND2H=W1,
+                                   Wl2_NHD=W2, group=dist.group.WORLD)
+        parallelism = "ep%d" % world
+    else:
+        Wg, W1, W2 = make_weights(1234, N, D, H, dev, N)
+        moe = momoe.MoE(D, H, N, K, Ks, save_percent=args.save_percent, Wg_DN=Wg, Wl1_ND2H=W1, Wl2_NHD=W2)
+        parallelism = "single"
+    del W1, W2
+    gen = torch.Generator(device="cpu").manual_seed(100 + rank)
+    x_host = torch.randn(c["B"], c["S"], D, generator=gen).bfloat16().pin_memory()
+    g_dev = torch.randn(c["B"], c["S"], D, generator=gen).bfloat16().to(dev)
+    x_dev = x_host.to(dev).requires_grad_(True)
+
+    def zero_grads():
+        for p in moe.parameters():
+            p.grad = None
+        x_dev.grad = None
+
+    def step_resident():
+        zero_grads()
+        y = moe(x_dev)
+        y.backward(g_dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------ device-resident throughput
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    ops.check_status(dev)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ops.KERNEL_EVENTS = []
+    launches0 = ops.LAUNCHES
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if sampler else None
+    launches = (ops.LAUNCHES - launches0) // args.steps
+    events, ops.KERNEL_EVENTS = ops.KERNEL_EVENTS, None
+    ops.check_status(dev)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    tokens_per_step = M * world
+    value = tokens_per_step / (ms * 1e-3)
+
+    # per-kernel device time from the events recorded inside the timed region
+    per = {}
+    for name, a, b in events:
+        per.setdefault(name, []).append(a.elapsed_time(b))
+    msum = M * K
+    unit_flops = float(msum) * D * H
+    # algorithmic flops of one launch, in units of Msum*D*H (up/gate 4, down 2, dgrad-2 2, wgrads 2 and 4, dgrad-1 4)
+    flops = {"momoe_up_swiglu": 4, "momoe_up_swiglu (recompute)": 4, "momoe_down_scale": 2,
+             "momoe_dgrad2_swiglu_bwd": 2, "momoe_wgrad (W2)": 2, "momoe_wgrad (W1)": 4, "momoe_dgrad1": 4}
+    peaks = measured_peaks()
+    kernels = []
+    for name, times in per.items():
+        avg = sum(times) / len(times)
+        k = dict(name=name, launches_per_step=len(times) // args.steps, ms=round(avg, 4))
+        if name in flops:
+            k["tflops"] = round(flops[name] * unit_flops / (avg * 1e-3) / 1e12, 1)
+        kernels.append(k)
+    kernels.sort(key=lambda k: -k["ms"] * k["launches_per_step"])
+    gemms = [k for k in kernels if "tflops" in k]
+    roofline = None
+    if gemms:
+        top = gemms[0]
+        roofline = dict(bound="tensor", kernel="grouped_gemm_kernel / " + top["name"], achieved=top["tflops"],
+                        peak=peaks["tflops"], unit="TFLOP/s", frac=round(top["tflops"] / peaks["tflops"], 4),
+                        traffic=None, peak_source=peaks["source"],
+                        flops_per_launch=flops[top["name"]] * unit_flops, ms_per_launch=top["ms"])
+    layer_flops = (18.0 * K * D * H + 6.0 * D * N) * M   # algorithmic fwd+bwd flops per rank and step
+    layer_tflops = layer_flops / (ms * 1e-3) / 1e12
+
+    # ------------------------------------------------------------------ end to end from pinned host memory
+    def step_e2e():
+        zero_grads()
+        with torch.no_grad():
+            x_dev.copy_(x_host, non_blocking=True)
+        y = moe(x_dev)
+        loss = torch.mean(torch.square(y.float()))
+        loss.backward()
+        return float(loss.item())   # device -> host read of the step's result
+
+    ms_e2e = float("nan")
+    if not args.no_e2e:
+        for _ in range(3):
+            step_e2e()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step_e2e()
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_e2e = float(t.item())
+    ops.check_status(dev)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cb = cpu_sample(2, 1)
+        cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = dict(
+            metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+            ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+            config=dict(workload=("REDUCED profiling case N%d tokens %d (not the headline workload)" % (N, M)) if reduced
+                        else "cfg2 headline layer: D2048 H1024 N128 K8, B8 S2048 (16384 tokens) per GPU, fwd+bwd",
+                        tokens_per_gpu=M, save_percent=args.save_percent, parallelism=parallelism,
+                        l2="inputs larger than L2 (weights 1.6 GB, activations > 0.5 GB per step)"),
+            e2e=dict(value=tokens_per_step / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e,
+                     h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=4),
+            gpu_launches=launches, clocks=clocks, roofline=roofline, cpu_baseline=cpu_baseline,
+            layer_tflops=round(layer_tflops, 1), layer_frac_of_peak=round(layer_tflops / peaks["tflops"], 4),
+            kernels=kernels)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

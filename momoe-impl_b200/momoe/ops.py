@@ -10,6 +10,27 @@ from ._lib import lib, ptr, stream_ptr, check
 TILE_M = 128
 _status_words = {}
 
+# Launch accounting.  LAUNCHES counts kernels queued through the C ABI; when KERNEL_EVENTS is a list, every call
+# is bracketed by CUDA events on the launching stream (used by the benchmark for per-kernel device times).
+LAUNCHES = 0
+KERNEL_EVENTS = None
+
+
+def _call(name, n_kernels, fn, *args):
+    global LAUNCHES
+    ev = KERNEL_EVENTS
+    if ev is not None:
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = fn(*args)
+        e1.record()
+        ev.append((name, e0, e1))
+    else:
+        rc = fn(*args)
+    check(rc, name)
+    LAUNCHES += n_kernels
+
 
 def status_word(device):
     """Per-device int32 word the kernels report device-side problems into (0 = fine)."""
@@ -77,12 +98,11 @@ class RoutingPlan:
         self.topk_idx, self.topk_w = topk_idx, topk_w
         nbytes = int(lib.momoe_permutation_workspace_bytes(self.M, self.N, self.K))
         ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=self.device)
-        check(lib.momoe_build_permutation(ptr(topk_idx), ptr(topk_w), self.M, self.N, self.K, self.save_rows,
+        _call("momoe_build_permutation", 3, lib.momoe_build_permutation, ptr(topk_idx), ptr(topk_w), self.M, self.N, self.K, self.save_rows,
                                           ptr(self.sizes), ptr(self.cumsums), ptr(self.idx), ptr(self.which),
                                           ptr(self.pad_off), ptr(self.tile_expert), ptr(self.sched),
                                           ptr(self.row_token), ptr(self.row_weight), ptr(self.pos),
-                                          self.rows_capacity, ptr(ws), nbytes, ptr(self.status), stream_ptr()),
-              "momoe_build_permutation")
+                                          self.rows_capacity, ptr(ws), nbytes, ptr(self.status), stream_ptr())
         return self
 
     @classmethod
@@ -102,9 +122,9 @@ class RoutingPlan:
         plan = cls(M, N, K, D, H, dev, save_percent)
         topk_idx = torch.empty((M, K), dtype=torch.int32, device=dev)
         topk_w = torch.empty((M, K), dtype=torch.float32, device=dev)
-        check(lib.momoe_topk_from_mask(ptr(mask_NM), mask_NM.stride(0), mask_NM.stride(1), ptr(s_NM),
+        _call("momoe_topk_from_mask", 1, lib.momoe_topk_from_mask, ptr(mask_NM), mask_NM.stride(0), mask_NM.stride(1), ptr(s_NM),
                                        s_NM.stride(0), s_NM.stride(1), M, N, K, ptr(topk_idx), ptr(topk_w),
-                                       ptr(plan.status), stream_ptr()), "momoe_topk_from_mask")
+                                       ptr(plan.status), stream_ptr())
         return plan.build(topk_idx, topk_w)
 
 
@@ -124,22 +144,22 @@ def route_topk(logits_MN, biases_N, K, Ks, dense=True):
                  s_postsoft_MN=torch.empty((M, N), dtype=torch.float32, device=dev),
                  Ng_M=torch.empty(M, dtype=torch.float32, device=dev),
                  Ks_M=torch.empty(M, dtype=torch.float32, device=dev))
-    check(lib.momoe_route_topk(ptr(logits_MN), ptr(biases_N), M, N, K, Ks, ptr(topk_idx), ptr(topk_w),
+    _call("momoe_route_topk", 1, lib.momoe_route_topk, ptr(logits_MN), ptr(biases_N), M, N, K, Ks, ptr(topk_idx), ptr(topk_w),
                                ptr(d["mask_NM"]) if d else None, ptr(d["s_MN"]) if d else None,
                                ptr(d["s_postsoft_MN"]) if d else None, ptr(d["Ng_M"]) if d else None,
-                               ptr(d["Ks_M"]) if d else None, stream_ptr()), "momoe_route_topk")
+                               ptr(d["Ks_M"]) if d else None, stream_ptr())
     return topk_idx, topk_w, d
 
 
 def gather_rows(plan, src, cols):
     dst = torch.empty((plan.rows_capacity, cols), dtype=torch.bfloat16, device=src.device)
-    check(lib.momoe_gather_rows(plan.ref, ptr(src), cols, ptr(dst), stream_ptr()), "momoe_gather_rows")
+    _call("momoe_gather_rows", 1, lib.momoe_gather_rows, plan.ref, ptr(src), cols, ptr(dst), stream_ptr())
     return dst
 
 
 def combine_rows(plan, src_sorted, cols):
     dst = torch.empty((plan.M, cols), dtype=torch.bfloat16, device=src_sorted.device)
-    check(lib.momoe_combine_rows(plan.ref, ptr(src_sorted), cols, ptr(dst), stream_ptr()), "momoe_combine_rows")
+    _call("momoe_combine_rows", 1, lib.momoe_combine_rows, plan.ref, ptr(src_sorted), cols, ptr(dst), stream_ptr())
     return dst
 
 
@@ -157,11 +177,11 @@ def experts_forward(plan, x_MD, W1, W2):
         a_save = torch.empty((plan.saved_tile_capacity * TILE_M, H), **bf)
         b_save = torch.empty((plan.saved_tile_capacity * TILE_M, H), **bf)
         mode = 1
-    check(lib.momoe_up_swiglu(plan.ref, ptr(x_sorted), ptr(W1), ptr(h), ptr(a_save), ptr(b_save), mode,
-                              stream_ptr()), "momoe_up_swiglu")
+    _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), ptr(h), ptr(a_save), ptr(b_save), mode,
+                              stream_ptr())
     del x_sorted
     y_sorted = torch.empty((plan.rows_capacity, D), **bf)
-    check(lib.momoe_down_scale(plan.ref, ptr(h), ptr(W2), ptr(y_sorted), stream_ptr()), "momoe_down_scale")
+    _call("momoe_down_scale", 1, lib.momoe_down_scale, plan.ref, ptr(h), ptr(W2), ptr(y_sorted), stream_ptr())
     y = combine_rows(plan, y_sorted, D)
     return y, a_save, b_save
 
@@ -177,26 +197,24 @@ def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=Tru
     if plan.recomp_tile_capacity > 0:
         a_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
         b_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
-        check(lib.momoe_up_swiglu(plan.ref, ptr(x_sorted), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2, stream_ptr()),
-              "momoe_up_swiglu (recompute)")
+        _call("momoe_up_swiglu (recompute)", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2, stream_ptr())
     n_part = (H + 127) // 128
     gz = torch.empty((plan.rows_capacity, 2 * H), **bf)
     hs = torch.empty((plan.rows_capacity, H), **bf)
     gs_part = torch.empty((plan.rows_capacity, n_part), dtype=torch.float32, device=dev)
-    check(lib.momoe_dgrad2_swiglu_bwd(plan.ref, ptr(g_sorted), ptr(W2), ptr(a_save), ptr(b_save), ptr(a_rec),
-                                      ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), stream_ptr()),
-          "momoe_dgrad2_swiglu_bwd")
+    _call("momoe_dgrad2_swiglu_bwd", 1, lib.momoe_dgrad2_swiglu_bwd, plan.ref, ptr(g_sorted), ptr(W2), ptr(a_save), ptr(b_save), ptr(a_rec),
+                                      ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), stream_ptr())
     del a_rec, b_rec
     G_W2 = torch.empty_like(W2)
-    check(lib.momoe_wgrad(plan.ref, ptr(hs), H, ptr(g_sorted), D, ptr(G_W2), stream_ptr()), "momoe_wgrad (W2)")
+    _call("momoe_wgrad (W2)", 1, lib.momoe_wgrad, plan.ref, ptr(hs), H, ptr(g_sorted), D, ptr(G_W2), stream_ptr())
     G_W1 = torch.empty_like(W1)
-    check(lib.momoe_wgrad(plan.ref, ptr(x_sorted), D, ptr(gz), 2 * H, ptr(G_W1), stream_ptr()), "momoe_wgrad (W1)")
+    _call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, plan.ref, ptr(x_sorted), D, ptr(gz), 2 * H, ptr(G_W1), stream_ptr())
     gx_sorted = g_sorted  # the gathered upstream gradient is dead after the W2 gradient; reuse its buffer
-    check(lib.momoe_dgrad1(plan.ref, ptr(gz), ptr(W1), ptr(gx_sorted), stream_ptr()), "momoe_dgrad1")
+    _call("momoe_dgrad1", 1, lib.momoe_dgrad1, plan.ref, ptr(gz), ptr(W1), ptr(gx_sorted), stream_ptr())
     G_x = combine_rows(plan, gx_sorted, D)
     if need_gs_dense:
         G_s = torch.empty((N, plan.M), dtype=torch.float32, device=dev)
-        check(lib.momoe_scatter_gs(plan.ref, ptr(gs_part), n_part, ptr(G_s), stream_ptr()), "momoe_scatter_gs")
+        _call("momoe_scatter_gs", 1, lib.momoe_scatter_gs, plan.ref, ptr(gs_part), n_part, ptr(G_s), stream_ptr())
     else:
         G_s = gs_part
     return G_x, G_W1, G_W2, G_s
@@ -207,7 +225,6 @@ def router_backward(G_s_NM, s_postsoft_MN, s_MN, Ng_M, Ks_M, mask_NM, Ks):
     if G_s_NM.dtype != torch.float32:
         G_s_NM = G_s_NM.to(torch.float32)
     out = torch.empty((M, N), dtype=torch.bfloat16, device=G_s_NM.device)
-    check(lib.momoe_router_backward(ptr(G_s_NM), G_s_NM.stride(0), G_s_NM.stride(1), ptr(s_postsoft_MN), ptr(s_MN),
-                                    ptr(Ng_M), ptr(Ks_M), ptr(mask_NM), M, N, Ks, ptr(out), stream_ptr()),
-          "momoe_router_backward")
+    _call("momoe_router_backward", 1, lib.momoe_router_backward, ptr(G_s_NM), G_s_NM.stride(0), G_s_NM.stride(1), ptr(s_postsoft_MN), ptr(s_MN),
+                                    ptr(Ng_M), ptr(Ks_M), ptr(mask_NM), M, N, Ks, ptr(out), stream_ptr())
     return out

@@ -278,29 +278,40 @@ def moe_forward_backward(x_BSD, Wg_DN, W1_ND2H, W2_NHD, biases_N, K, Ks, save_pe
 # ----------------------------------------------------------------------------------------------------
 # Throughput-oriented variant for the CPU baseline timing (same math, autograd backward)
 # ----------------------------------------------------------------------------------------------------
-def cpu_baseline_step(x_BSD, Wg_DN, W1_ND2H, W2_NHD, biases_N, K, Ks):
+def cpu_baseline_prepare(Wg_DN, W1_ND2H, W2_NHD):
+    """fp32 per-expert leaf weights (views of one buffer, so a gradient is only materialised for experts that
+    received tokens).  Done once, outside the timed region."""
+    W1 = W1_ND2H.to(f32)
+    W2 = W2_NHD.to(f32)
+    return dict(Wg=Wg_DN.to(f32).requires_grad_(True),
+                W1=[w.detach().requires_grad_(True) for w in W1.unbind(0)],
+                W2=[w.detach().requires_grad_(True) for w in W2.unbind(0)])
+
+
+def cpu_baseline_step(state, x_BSD, biases_N, K, Ks):
     """One fwd+bwd of the layer on the host cores: sparse per-expert index_select -> matmuls -> SiLU*mul ->
     matmul -> index_add_, autograd for the backward, all available torch threads.  Follows
     momoe/sample_moe.py:59-68 and the math of momoe/momoe.py; used only as the timed CPU baseline."""
     B, S, D = x_BSD.shape
     M = B * S
-    N, H, _ = W2_NHD.shape
+    W1, W2, Wg = state["W1"], state["W2"], state["Wg"]
+    N = len(W1)
+    H = W2[0].shape[0]
+    for w in W1 + W2 + [Wg]:
+        w.grad = None
     x = x_BSD.reshape(M, D).to(f32).requires_grad_(True)
-    W1 = W1_ND2H.to(f32).requires_grad_(True)
-    W2 = W2_NHD.to(f32).requires_grad_(True)
-    Wg = Wg_DN.to(f32).requires_grad_(True)
     raw = x @ Wg
     Ng = N - Ks
     p = torch.softmax(raw[:, :Ng], dim=-1)
     sel = torch.topk(p.detach() + biases_N[:Ng][None, :], K - Ks, dim=-1).indices
     q = torch.gather(p, 1, sel)
     w_sel = q / q.sum(-1, keepdim=True)
-    y = torch.zeros((M, D), dtype=f32)
     flat_e = sel.reshape(-1)
     order = torch.argsort(flat_e, stable=True)
     counts = torch.bincount(flat_e, minlength=Ng)
-    tok = (order // (K - Ks))
+    tok = order // (K - Ks)
     wflat = w_sel.reshape(-1)[order]
+    parts, rows_all = [], []
     start = 0
     for e in range(Ng):
         c = int(counts[e])
@@ -309,8 +320,10 @@ def cpu_baseline_step(x_BSD, Wg_DN, W1_ND2H, W2_NHD, biases_N, K, Ks):
         rows = tok[start:start + c]
         z = x.index_select(0, rows) @ W1[e]
         hh = z[:, :H] * torch.nn.functional.silu(z[:, H:])
-        y = y.index_add(0, rows, (hh @ W2[e]) * wflat[start:start + c, None])
+        parts.append((hh @ W2[e]) * wflat[start:start + c, None])
+        rows_all.append(rows)
         start += c
+    y = torch.zeros((M, D), dtype=f32).index_add(0, torch.cat(rows_all), torch.cat(parts))
     if Ks > 0:
         ps = torch.softmax(raw[:, Ng:], dim=-1)
         for j in range(Ks):
