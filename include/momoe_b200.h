@@ -80,6 +80,25 @@ int momoe_build_permutation(const int32_t* topk_idx_MK, const float* topk_w_MK, 
                             int32_t* row_token, float* row_weight, int32_t* pos_MK, int64_t rows_capacity,
                             void* workspace, size_t workspace_bytes, int32_t* status, momoe_stream_t stream);
 
+/* The same permutation builder for callers that cannot provide a workspace.  It has no counterpart in the
+ * reference.  Some hosts of this library are not able to allocate device memory when they route tokens: an
+ * inference server whose own pool took all of HBM at start-up, a latency-critical loop that must avoid the device
+ * synchronisation an allocation implies, a plug-in that only ever receives its input and output tensors.  Here
+ * the chunk histogram lives in a 1 MiB array inside the library image (every GPU that loads the library holds
+ * that 1 MiB until the process exits), and the call allocates nothing.
+ *   Limit: ceil(M/64) * N <= 262144 (for example 65536 tokens x 256 experts); larger problems return -4 and
+ *   launch nothing.  All other arguments, outputs and return codes are those of momoe_build_permutation.
+ *   The first call on each device looks up the array's device address (a runtime call that may load the module):
+ *   make that first call outside any stream capture.
+ *   All calls on a device share the one array and it keeps the last call's contents; the kernels overwrite every
+ *   entry they later read, so nothing needs clearing, but two calls that overlap on the GPU (different streams
+ *   without ordering between them) race on it and corrupt each other's result. */
+int momoe_build_permutation_static(const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N,
+                                   int32_t K, int64_t save_rows, int64_t* sizes_N, int32_t* cumsums_N1,
+                                   int32_t* idx_Msum, int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert,
+                                   int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
+                                   int64_t rows_capacity, int32_t* status, momoe_stream_t stream);
+
 /* dst[r,:] = src[row_token[r],:] (zeros on padding rows), bf16, `cols` columns (multiple of 8).
  * Replaces the row gathers of momoe/momoe.py:116-118 and :298-350. */
 int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,

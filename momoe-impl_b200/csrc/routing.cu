@@ -2,6 +2,7 @@
 // backward helpers.  All of this is HBM-bound integer / byte work: warp-level kernels, 128-bit accesses.
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "internal.h"
 #include "../../include/momoe_b200.h"
@@ -572,5 +573,78 @@ extern "C" __attribute__((visibility("default"))) int momoe_router_backward(cons
     router_backward_kernel<<<cdiv(M, warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         G_s, gs_stride_n, gs_stride_m, s_postsoft_MN, s_MN, Ng_M, Ks_M, mask_NM, M, N, Ks,
         static_cast<__nv_bfloat16*>(G_logits_MN));
+    return LAUNCH_OK();
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Permutation builder for callers that cannot hand over a scratch buffer.
+//
+// momoe_build_permutation needs a caller-allocated workspace for the per-chunk histogram.  Some callers have no
+// way to obtain one at the moment they route tokens: a serving engine that gave all of HBM to its own pool at
+// start-up and must not call cudaMalloc afterwards, a real-time loop that cannot afford the implicit device
+// synchronisation of an allocation, or a plug-in that is only ever handed its input and output tensors.  For
+// them the histogram lives in a fixed array inside the library image.  The array occupies device memory on every
+// GPU that loads the library, from load until the process exits, so it is kept small (1 MiB).
+namespace momoe {
+
+constexpr long long kStaticPermScratchInts = 262144;  // 1 MiB of int32: ceil(M/64) * N must not exceed this
+
+// The histogram itself.  On the host this name is only a handle for the runtime: taking its address in host code
+// does not give a device pointer (a kernel handed that value would fault, or on systems where the GPU can reach
+// host memory, silently use the wrong bytes).  The device address is looked up with cudaGetSymbolAddress below.
+static __device__ __align__(256) int g_perm_scratch[kStaticPermScratchInts];
+
+static std::mutex g_perm_scratch_mu;
+static int* g_perm_scratch_dev[64] = {nullptr};  // resolved device address, per device ordinal
+
+// Device address of g_perm_scratch on the CURRENT device; resolved once per device.
+static int perm_scratch_address(int** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MOMOE_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(g_perm_scratch_mu);
+    if (g_perm_scratch_dev[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_perm_scratch) != cudaSuccess || p == nullptr) return MOMOE_ERR_CUDA;
+        g_perm_scratch_dev[dev] = static_cast<int*>(p);
+    }
+    *out = g_perm_scratch_dev[dev];
+    return MOMOE_OK;
+}
+
+}  // namespace momoe
+
+extern "C" __attribute__((visibility("default"))) int momoe_build_permutation_static(
+    const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N, int32_t K, int64_t save_rows,
+    int64_t* sizes_N, int32_t* cumsums_N1, int32_t* idx_Msum, int32_t* which_Msum, int32_t* pad_off,
+    int32_t* tile_expert, int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
+    int64_t rows_capacity, int32_t* status, momoe_stream_t stream) {
+    if (topk_idx_MK == nullptr || topk_w_MK == nullptr || sizes_N == nullptr || cumsums_N1 == nullptr ||
+        idx_Msum == nullptr || which_Msum == nullptr || pad_off == nullptr || tile_expert == nullptr ||
+        sched == nullptr || row_token == nullptr || row_weight == nullptr || pos_MK == nullptr || status == nullptr)
+        return MOMOE_ERR_ARG;
+    if (M <= 0 || N <= 0 || K <= 0 || K > N || save_rows < 0) return MOMOE_ERR_ARG;
+    if (N > MAX_EXPERTS || K > MAX_TOPK) return MOMOE_ERR_TOO_LARGE;
+    if (static_cast<int64_t>(M) * K > 0x7fffffffLL - static_cast<int64_t>(N) * TILE_M) return MOMOE_ERR_TOO_LARGE;
+    if (rows_capacity < momoe_sorted_rows_capacity(M, K, N)) return MOMOE_ERR_ARG;
+    const long long n_chunks = (static_cast<long long>(M) + CHUNK_TOKENS - 1) / CHUNK_TOKENS;
+    if (n_chunks * N > kStaticPermScratchInts) return MOMOE_ERR_TOO_LARGE;  // histogram would not fit the fixed array
+    int* counts = nullptr;
+    const int rc = perm_scratch_address(&counts);
+    if (rc != MOMOE_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int warps = 4;
+    const int blocks = cdiv(n_chunks, warps);
+    if (cudaMemsetAsync(row_token, 0xFF, sizeof(int32_t) * static_cast<size_t>(rows_capacity), st) != cudaSuccess ||
+        cudaMemsetAsync(row_weight, 0, sizeof(float) * static_cast<size_t>(rows_capacity), st) != cudaSuccess)
+        return MOMOE_ERR_CUDA;
+    // The array still holds the previous call's histogram.  Nothing has to be cleared: the first pass overwrites
+    // every entry [chunk, expert] of the part this call uses before the later passes read it.
+    perm_count_kernel<<<blocks, warps * 32, warps * N * sizeof(int), st>>>(topk_idx_MK, M, N, K, counts, status);
+    perm_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(counts, static_cast<int>(n_chunks), M, N, K, save_rows,
+                                                reinterpret_cast<long long*>(sizes_N), cumsums_N1, pad_off,
+                                                tile_expert, sched, static_cast<int>(momoe_tile_capacity(M, K, N)));
+    perm_fill_kernel<<<blocks, warps * 32, warps * 2 * N * sizeof(int), st>>>(
+        topk_idx_MK, topk_w_MK, counts, cumsums_N1, pad_off, M, N, K, idx_Msum, which_Msum, row_token, row_weight,
+        pos_MK);
     return LAUNCH_OK();
 }

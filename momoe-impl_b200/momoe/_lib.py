@@ -40,6 +40,8 @@ _PROTOS = {
     "momoe_permutation_workspace_bytes": (c_sz, [c_i32, c_i32, c_i32]),
     "momoe_build_permutation": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                                           c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_sz, c_vp, c_vp]),
+    "momoe_build_permutation_static": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp,
+                                                 c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
     "momoe_gather_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_combine_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_up_swiglu": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
