@@ -241,6 +241,13 @@ def main():
     # algorithmic flops of one launch, in units of Msum*D*H (up/gate 4, down 2, dgrad-2 2, wgrads 2 and 4, dgrad-1 4)
     flops = {"momoe_up_swiglu": 4, "momoe_up_swiglu (recompute)": 4, "momoe_down_scale": 2,
              "momoe_dgrad2_swiglu_bwd": 2, "momoe_wgrad (W2)": 2, "momoe_wgrad (W1)": 4, "momoe_dgrad1": 4}
+    # DRAM bytes per launch (read + write) from the ncu capture summarised in
+    # profiles/grouped_gemm_reduced_case_ncu_full.md (32 experts, 4096 tokens), per (expert x token) unit; traffic
+    # grows in proportion to both, so it is scaled to this run's experts and tokens.
+    ncu_mb_small = {"momoe_up_swiglu": 471, "momoe_up_swiglu (recompute)": 537, "momoe_down_scale": 309,
+                    "momoe_dgrad2_swiglu_bwd": 600, "momoe_wgrad (W2)": 316, "momoe_wgrad (W1)": 511,
+                    "momoe_dgrad1": 532}
+    traffic_scale = 0.5 * (N / 32.0 + M / 4096.0)
     peaks = measured_peaks()
     kernels = []
     for name, times in per.items():
@@ -256,7 +263,8 @@ def main():
         top = gemms[0]
         roofline = dict(bound="tensor", kernel="grouped_gemm_kernel / " + top["name"], achieved=top["tflops"],
                         peak=peaks["tflops"], unit="TFLOP/s", frac=round(top["tflops"] / peaks["tflops"], 4),
-                        traffic=None, peak_source=peaks["source"],
+                        traffic=ncu_mb_small[top["name"]] * 1e6 * traffic_scale, peak_source=peaks["source"],
+                        traffic_note="dram__bytes_read+write per launch from an ncu capture of a 1/4-size case, scaled",
                         flops_per_launch=flops[top["name"]] * unit_flops, ms_per_launch=top["ms"])
     layer_flops = (18.0 * K * D * H + 6.0 * D * N) * M   # algorithmic fwd+bwd flops per rank and step
     layer_tflops = layer_flops / (ms * 1e-3) / 1e12
