@@ -1,0 +1,220 @@
+"""Expert parallelism for the MoMoE layer (the reference has none; its README lists it as unsupported).
+
+Rank r of an R-rank group owns the contiguous expert block [r*N/R, (r+1)*N/R) and keeps its own tokens
+(data parallel).  One forward pass does
+
+    route locally -> gather rows into expert-major order (already grouped by destination rank)
+    -> all-gather of the per-expert counts (the only host synchronisation: NCCL needs split sizes)
+    -> all-to-all of rows and routing weights -> local grouped GEMMs on the received rows
+    -> all-to-all back -> combine at the token's home rank.
+
+Backward mirrors it with the upstream gradient.  Payload always lands in the receiving GPU's own memory and is
+read from there by the local kernels; no kernel touches a peer's memory.
+
+`DispatchMeta` holds the pure index arithmetic (device-agnostic torch ops), so it is testable with CPU ranks.
+"""
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .topk_router import TopKRouter
+
+
+class DispatchMeta:
+    """Index arithmetic of one dispatch, built from this rank's routing and the all-gathered counts.
+
+    sizes_RN  int64 [R, N]  tokens rank s routes to global expert e (row s = rank s's `sizes_N`)
+    idx, which int32 [M*K]  this rank's expert-major permutation (token of each row, slot of each row)
+    """
+
+    def __init__(self, sizes_RN, idx, which, rank, M, K):
+        R, N = sizes_RN.shape
+        assert N % R == 0, "experts must divide evenly across ranks"
+        self.R, self.N, self.Nl, self.rank, self.M, self.K = R, N, N // R, rank, M, K
+        per_block = sizes_RN.view(R, R, self.Nl).sum(-1)               # [source, destination]
+        self.send_splits = per_block[rank].tolist()                    # rows this rank sends to each rank
+        self.recv_splits = per_block[:, rank].tolist()                 # rows this rank receives from each rank
+        self.n_send = int(sum(self.send_splits))
+        self.n_recv = int(sum(self.recv_splits))
+        assert self.n_send == M * K
+        dev = idx.device
+        # local expert (0..Nl-1) of every received row: source-major, inside a source expert-major
+        mine = sizes_RN[:, rank * self.Nl:(rank + 1) * self.Nl].reshape(-1).to(dev)
+        self.recv_expert = torch.arange(self.Nl, device=dev, dtype=torch.int32).repeat(R).repeat_interleave(
+            mine, output_size=self.n_recv)
+        # row of token m's k-th expert in the (unpadded) send order
+        self.pos_unpadded = torch.empty(M * K, dtype=torch.int32, device=dev)
+        self.pos_unpadded[idx.long() * K + which.long()] = torch.arange(M * K, dtype=torch.int32, device=dev)
+        # global expert of every sent row (for the dense G_s the router backward consumes)
+        self.send_expert = torch.arange(N, device=dev).repeat_interleave(sizes_RN[rank].to(dev), output_size=M * K)
+        self.global_sizes = sizes_RN.sum(0)
+
+
+def exchange(t_send, send_splits, recv_splits, group):
+    """all-to-all-v over rows of a [rows, ...] tensor."""
+    out = t_send.new_empty((int(sum(recv_splits)),) + tuple(t_send.shape[1:]))
+    dist.all_to_all_single(out, t_send.contiguous(), recv_splits, send_splits, group=group)
+    return out
+
+
+def gather_counts(sizes_N, group):
+    R = dist.get_world_size(group)
+    out = torch.empty(R * sizes_N.numel(), dtype=sizes_N.dtype, device=sizes_N.device)
+    dist.all_gather_into_tensor(out, sizes_N.contiguous(), group=group)
+    return out.view(R, sizes_N.numel()).cpu()   # host copy: NCCL split sizes are host integers
+
+
+class _Rows:
+    """Row movers on the device through the C ABI, addressed with ad-hoc row tables."""
+
+    @staticmethod
+    def gather(src, row_index, n_rows):
+        """dst[r] = src[row_index[r]] for r < n_rows (bf16 rows)."""
+        from . import _lib, ops
+        cols = src.shape[1]
+        dst = torch.empty((n_rows, cols), dtype=torch.bfloat16, device=src.device)
+        if n_rows == 0:
+            return dst
+        sched = torch.tensor([0, 0, n_rows, 0, 0, 0, 0, 0], dtype=torch.int32, device=src.device)
+        plan = _lib.Plan(M=1, N=1, K=1, D=cols, H=8, reserved=0, rows_capacity=128, sched=sched.data_ptr(),
+                         tile_expert=0, pad_off=0, row_token=row_index.data_ptr(), row_weight=0, pos_MK=0, status=0)
+        ops._call("momoe_gather_rows", 1, _lib.lib.momoe_gather_rows, C.byref(plan), _lib.ptr(src), cols,
+                  _lib.ptr(dst), _lib.stream_ptr())
+        return dst
+
+    @staticmethod
+    def combine(src, pos_MK, M, K):
+        """dst[m] = bf16(sum_k src[pos_MK[m, k]])."""
+        from . import _lib, ops
+        cols = src.shape[1]
+        dst = torch.empty((M, cols), dtype=torch.bfloat16, device=src.device)
+        plan = _lib.Plan(M=M, N=1, K=K, D=cols, H=8, reserved=0, rows_capacity=128, sched=0, tile_expert=0, pad_off=0,
+                         row_token=0, row_weight=0, pos_MK=pos_MK.data_ptr(), status=0)
+        ops._call("momoe_combine_rows", 1, _lib.lib.momoe_combine_rows, C.byref(plan), _lib.ptr(src), cols,
+                  _lib.ptr(dst), _lib.stream_ptr())
+        return dst
+
+
+class ExpertParallelFunction(torch.autograd.Function):
+    """Forward / backward of the expert computation with dispatch and combine over the process group."""
+
+    @staticmethod
+    def forward(ctx, x_BSD, W1_local, W2_local, mask_NM, s_NM, topk_idx, topk_w, K, save_percent, group):
+        from . import ops
+        B, S, D = x_BSD.shape
+        M = B * S
+        dev = W1_local.device
+        Nl, H, _ = W2_local.shape
+        R = dist.get_world_size(group)
+        rank = dist.get_rank(group)
+        N = Nl * R
+        x_MD = x_BSD.reshape(M, D).to(device=dev, dtype=torch.bfloat16).contiguous()
+        W1 = W1_local.detach().to(torch.bfloat16).contiguous()
+        W2 = W2_local.detach().to(torch.bfloat16).contiguous()
+        with torch.cuda.device(dev):
+            home = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, H, 0.0)     # permutation over all N experts
+            sizes_RN = gather_counts(home.sizes, group)
+            meta = DispatchMeta(sizes_RN, home.idx, home.which, rank, M, K)
+            x_send = _Rows.gather(x_MD, home.idx, meta.n_send)
+            w_send = topk_w.reshape(-1)[(home.idx.long() * K + home.which.long())].contiguous()
+            x_recv = exchange(x_send, meta.send_splits, meta.recv_splits, group)
+            w_recv = exchange(w_send, meta.send_splits, meta.recv_splits, group)
+            del x_send
+            # the received rows are this rank's "tokens", each routed to exactly one local expert
+            if meta.n_recv > 0:
+                local = ops.RoutingPlan.from_topk(meta.recv_expert.view(-1, 1), w_recv.view(-1, 1), Nl, D, H,
+                                                  save_percent)
+                y_recv, a_save, b_save = ops.experts_forward(local, x_recv, W1, W2)
+            else:
+                local, a_save, b_save = None, None, None
+                y_recv = x_recv
+            y_back = exchange(y_recv, meta.recv_splits, meta.send_splits, group)
+            y_MD = _Rows.combine(y_back, meta.pos_unpadded, M, K)
+        ctx.group, ctx.meta, ctx.home, ctx.local = group, meta, home, local
+        ctx.shape = (B, S, D)
+        ctx.dims = (N, Nl, H, K)
+        ctx.in_devices = (x_BSD.device, s_NM.device)
+        ctx.has_ab = a_save is not None
+        saved = [x_recv, W1, W2] + ([a_save, b_save] if ctx.has_ab else [])
+        ctx.save_for_backward(*saved)
+        sizes_global = meta.global_sizes.to(dev)
+        ctx.mark_non_differentiable(sizes_global)
+        return y_MD.reshape(B, S, D).to(x_BSD.device), sizes_global
+
+    @staticmethod
+    def backward(ctx, G_y_BSD, _):
+        from . import ops
+        saved = ctx.saved_tensors
+        x_recv, W1, W2 = saved[:3]
+        a_save, b_save = (saved[3], saved[4]) if ctx.has_ab else (None, None)
+        B, S, D = ctx.shape
+        N, Nl, H, K = ctx.dims
+        M = B * S
+        meta, home, local, group = ctx.meta, ctx.home, ctx.local, ctx.group
+        dev = W1.device
+        g_MD = G_y_BSD.reshape(M, D).to(device=dev, dtype=torch.bfloat16).contiguous()
+        with torch.cuda.device(dev):
+            g_send = _Rows.gather(g_MD, home.idx, meta.n_send)
+            g_recv = exchange(g_send, meta.send_splits, meta.recv_splits, group)
+            del g_send
+            if local is not None:
+                gx_recv, G_W1, G_W2, gs_part = ops.experts_backward(local, g_recv, x_recv, W1, W2, a_save, b_save,
+                                                                    need_gs_dense=False)
+                gs_recv = gs_part.sum(-1)[local.pos.long()].contiguous()      # K = 1: pos[j] is row j's padded row
+            else:
+                gx_recv = g_recv
+                G_W1, G_W2 = torch.zeros_like(W1), torch.zeros_like(W2)
+                gs_recv = torch.empty(0, dtype=torch.float32, device=dev)
+            gx_back = exchange(gx_recv, meta.recv_splits, meta.send_splits, group)
+            gs_back = exchange(gs_recv, meta.recv_splits, meta.send_splits, group)
+            G_x = _Rows.combine(gx_back, meta.pos_unpadded, M, K)
+            G_s = torch.zeros((N, M), dtype=torch.float32, device=dev)
+            G_s[meta.send_expert, home.idx.long()] = gs_back
+        x_dev, s_dev = ctx.in_devices
+        return (G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_s.to(s_dev), None, None, None, None, None)
+
+
+class ExpertParallelMoE(nn.Module):
+    """`MoE` with the experts sharded over a process group: same forward signature and bias update; the router is
+    replicated, `Wl1_ND2H` / `Wl2_NHD` hold this rank's block of N/R experts, and `tokens_per_expert_N` (which drives
+    the bias update) is the global count summed over ranks."""
+
+    def __init__(self, embedding_dim, intermediate_dim, num_experts, num_chosen_experts, num_shared_experts,
+                 save_percent=0, bias_update_rate=1e-4, Wg_DN=None, Wl1_ND2H=None, Wl2_NHD=None, *, group=None):
+        super().__init__()
+        assert save_percent >= 0 and save_percent <= 100, \
+            "save_percent must be between 0 and 100 inclusive, got {}".format(save_percent)
+        self.group = group if group is not None else dist.group.WORLD
+        R = dist.get_world_size(self.group)
+        assert num_experts % R == 0, "num_experts must be divisible by the number of ranks"
+        self.D, self.H, self.N, self.K, self.Ks = (embedding_dim, intermediate_dim, num_experts, num_chosen_experts,
+                                                   num_shared_experts)
+        self.save_percent = save_percent
+        self.bias_update_rate = bias_update_rate
+        Nl = num_experts // R
+        self.router = TopKRouter(embedding_dim, num_experts, num_chosen_experts, num_shared_experts, Wg_DN=Wg_DN)
+        dev = self.router.Wg_DN.device
+        if Wl1_ND2H is None:
+            Wl1_ND2H = torch.randn((Nl, self.D, 2 * self.H), device=dev, dtype=torch.bfloat16) / self.D
+        if Wl2_NHD is None:
+            Wl2_NHD = torch.randn((Nl, self.H, self.D), device=dev, dtype=torch.bfloat16) / self.D
+        assert Wl1_ND2H.shape[0] == Nl and Wl2_NHD.shape[0] == Nl, "pass this rank's block of N/R experts"
+        self.Wl1_ND2H = nn.Parameter(Wl1_ND2H.clone().detach().to(torch.bfloat16), requires_grad=True)
+        self.Wl2_NHD = nn.Parameter(Wl2_NHD.clone().detach().to(torch.bfloat16), requires_grad=True)
+        self.biases_N = nn.Parameter(
+            torch.cat([torch.zeros(self.N - self.Ks, device=dev, dtype=torch.float32),
+                       torch.full((self.Ks,), float("-inf"), device=dev, dtype=torch.float32)], dim=-1),
+            requires_grad=False)
+
+    def forward(self, x_BSD):
+        x_BSD, mask_NM, s_NM = self.router(x_BSD, self.biases_N)
+        topk_idx, topk_w = mask_NM._momoe_topk
+        y_BSD, sizes_N = ExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM, topk_idx,
+                                                      topk_w, self.K, self.save_percent, self.group)
+        B, S, _ = x_BSD.shape
+        R = dist.get_world_size(self.group)
+        c_avg = B * S * R * (self.K - self.Ks) / (self.N - self.Ks)
+        self.biases_N += self.bias_update_rate * torch.sign(c_avg - sizes_N.to(self.biases_N.device))
+        return y_BSD

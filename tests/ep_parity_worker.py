@@ -1,0 +1,82 @@
+"""Worker of the multi-GPU expert-parallel parity test (launched by torchrun, one rank per GPU).
+
+Every rank builds the same seeded global problem, runs (a) the single-GPU `MoE` on ALL tokens with ALL experts and
+(b) `ExpertParallelMoE` on its own token shard with its own expert block, and compares: y and dX of its shard,
+dW of its expert block, the summed gate gradient, the global tokens_per_expert and the bias update."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "momoe-impl_b200"))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    import momoe
+    from momoe import ep, ops
+    from helpers import cos, max_rel
+
+    cases = [  # tokens per rank, D, H, N, K, Ks, save_percent, bias_std
+        (192, 256, 128, 8, 2, 0, 0, 0.0),
+        (1000, 512, 256, 16, 4, 0, 50, 0.05),
+        (512, 384, 136, 8, 3, 1, 100, 0.02),
+    ]
+    for (Mr, D, H, N, K, Ks, sp, bias_std) in cases:
+        g = torch.Generator().manual_seed(1234 + D)
+        x_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
+        W1 = (torch.randn(N, D, 2 * H, generator=g) * 0.03).bfloat16()
+        W2 = (torch.randn(N, H, D, generator=g) * 0.03).bfloat16()
+        Wg = (torch.randn(D, N, generator=g) * 0.05).bfloat16()
+        gy_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
+        biases = torch.cat([torch.randn(N - Ks, generator=g) * bias_std, torch.full((Ks,), float("-inf"))])
+        Nl = N // world
+        # (a) single GPU, all tokens
+        ref = momoe.MoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
+                        Wl1_ND2H=W1.to(dev), Wl2_NHD=W2.to(dev))
+        with torch.no_grad():
+            ref.biases_N.copy_(biases.to(dev))
+        xa = x_all.reshape(1, world * Mr, D).to(dev).requires_grad_(True)
+        ya = ref(xa)
+        ya.backward(gy_all.reshape(1, world * Mr, D).to(dev))
+        # (b) expert parallel, own shard
+        moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
+                                   Wl1_ND2H=W1[rank * Nl:(rank + 1) * Nl].to(dev),
+                                   Wl2_NHD=W2[rank * Nl:(rank + 1) * Nl].to(dev))
+        with torch.no_grad():
+            moe.biases_N.copy_(biases.to(dev))
+        xr = x_all[rank].to(dev).requires_grad_(True)
+        yr = moe(xr)
+        yr.backward(gy_all[rank].to(dev))
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        sl = slice(rank * Mr, (rank + 1) * Mr)
+        assert torch.equal(moe.biases_N, ref.biases_N), "bias update (global tokens_per_expert) differs"
+        # same kernels, same per-row arithmetic: y rows are identical bits
+        assert torch.equal(yr[0], ya[0, sl]), "y differs: max-rel %g" % max_rel(yr[0], ya[0, sl])
+        assert cos(xr.grad[0], xa.grad[0, sl]) > 0.9999 and max_rel(xr.grad[0], xa.grad[0, sl]) < 2e-2
+        for name, got, full in (("W1", moe.Wl1_ND2H.grad, ref.momoe.Wl1_ND2H.grad),
+                                ("W2", moe.Wl2_NHD.grad, ref.momoe.Wl2_NHD.grad)):
+            want = full[rank * Nl:(rank + 1) * Nl]
+            assert cos(got, want) > 0.9999, name
+            assert max_rel(got, want) < 2e-2, name
+        gwg = moe.router.Wg_DN.grad.float().clone()
+        dist.all_reduce(gwg)
+        assert cos(gwg, ref.router.Wg_DN.grad) > 0.999
+        if rank == 0:
+            print("ep parity ok:", (Mr, D, H, N, K, Ks, sp), "world", world, flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,106 @@
+"""Expert-parallel dispatch metadata with two CPU ranks (gloo): rows reach the rank that owns their expert, arrive in
+source-major / expert-major order, and return to the slot they left from."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import momoe_oracle as orc
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _routing(rank, M, N, K):
+    g = torch.Generator().manual_seed(100 + rank)
+    logits = torch.randn(M, N, generator=g) + (torch.arange(N) % 3 == 0) * 1.5     # skewed
+    sel = torch.topk(logits, K, dim=-1).indices
+    mask = torch.zeros(M, N, dtype=torch.int32).scatter_(1, sel, 1).T.contiguous()
+    sizes, cumsums, idx, which = orc.permutation_from_mask(mask.numpy(), K)
+    return torch.from_numpy(sizes), torch.from_numpy(idx), torch.from_numpy(which), mask
+
+
+def _worker(rank, world, port, M, N, K, D):
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(os.path.dirname(here), "momoe-impl_b200"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from momoe import ep
+    sizes, idx, which, mask = _routing(rank, M, N, K)
+    Nl = N // world
+    sizes_RN = ep.gather_counts(sizes, dist.group.WORLD)
+    assert sizes_RN.shape == (world, N) and torch.equal(sizes_RN[rank], sizes)
+    meta = ep.DispatchMeta(sizes_RN, idx, which, rank, M, K)
+    assert sum(meta.send_splits) == M * K
+    assert torch.equal(meta.global_sizes, sizes_RN.sum(0))
+    # payload: [global expert, source rank, token, value]
+    x = torch.randn(M, D, generator=torch.Generator().manual_seed(7 + rank))
+    expert_of_row = torch.from_numpy(np.nonzero(mask.numpy())[0])
+    assert torch.equal(meta.send_expert, expert_of_row)
+    tag = torch.stack([expert_of_row.float(), torch.full((M * K,), float(rank)), idx.float()], dim=1)
+    send = torch.cat([tag, x[idx.long()]], dim=1)
+    recv = ep.exchange(send, meta.send_splits, meta.recv_splits, dist.group.WORLD)
+    assert recv.shape[0] == meta.n_recv == int(sizes_RN[:, rank * Nl:(rank + 1) * Nl].sum())
+    # every received row belongs to one of this rank's experts, and recv_expert names it
+    assert torch.equal(recv[:, 0].long() - rank * Nl, meta.recv_expert.long())
+    # source-major, then expert-major, then ascending token
+    key = recv[:, 1].double() * 1e9 + recv[:, 0].double() * 1e5 + recv[:, 2].double()
+    assert torch.all(key[1:] > key[:-1])
+    # "expert" e multiplies by (e + 1); send back and combine at home
+    y_recv = recv[:, 3:] * (recv[:, 0:1] + 1.0)
+    y_back = ep.exchange(y_recv, meta.recv_splits, meta.send_splits, dist.group.WORLD)
+    pos = meta.pos_unpadded.view(M, K).long()
+    y = y_back[pos].sum(1)
+    expect = x * (mask.T.float() @ (torch.arange(N).float() + 1.0))[:, None]
+    torch.testing.assert_close(y, expect, rtol=1e-5, atol=1e-5)
+    # slot k of token m is its k-th expert in ascending id
+    assert torch.equal(expert_of_row[pos], torch.sort(torch.nonzero(mask.T)[:, 1].view(M, K), dim=1).values)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,M,N,K", [(2, 50, 8, 2), (2, 33, 6, 3), (4, 40, 8, 4)])
+def test_dispatch_round_trip_gloo(world, M, N, K):
+    mp.spawn(_worker, args=(world, _free_port(), M, N, K, 5), nprocs=world, join=True)
+
+
+def _failing_worker(rank, world, port):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        # this rank dies between steps, before the counts exchange
+        os._exit(0)
+    t = torch.zeros(4, dtype=torch.int64)
+    out = torch.empty(world * 4, dtype=torch.int64)
+    try:
+        dist.all_gather_into_tensor(out, t)
+    except Exception:
+        os._exit(0)     # the surviving rank got an error instead of hanging
+    os._exit(3)
+
+
+def test_missing_rank_ends_counts_exchange_with_an_error():
+    """A rank that leaves before the counts all-gather must make its peer fail within the group timeout."""
+    ctx = mp.spawn(_failing_worker, args=(2, _free_port()), nprocs=2, join=False)
+    import time
+    deadline = time.time() + 90
+    while time.time() < deadline and any(p.exitcode is None for p in ctx.processes):
+        time.sleep(0.2)
+    codes = [p.exitcode for p in ctx.processes]
+    for p in ctx.processes:
+        if p.is_alive():
+            p.kill()
+    assert codes == [0, 0], codes
