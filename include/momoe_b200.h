@@ -36,13 +36,17 @@ typedef struct momoe_plan {
     int32_t H;                   /* intermediate dim */
     int32_t reserved;
     int64_t rows_capacity;       /* rows of every expert-major buffer (momoe_sorted_rows_capacity) */
-    const int32_t* sched;        /* int32[8]: [0] 128-row tiles in use, [1] tiles whose a,b are saved, [2] padded rows */
+    const int32_t* sched;        /* int32[8]: [0] 128-row tiles in use, [1] tiles whose a,b are saved, [2] padded rows,
+                                    [3] tile pairs */
     const int32_t* tile_expert;  /* int32[momoe_tile_capacity]: expert of each tile */
     const int32_t* pad_off;      /* int32[N+1]: first padded row of each expert */
     const int32_t* row_token;    /* int32[rows_capacity]: token of each padded row, -1 on padding rows */
     const float* row_weight;     /* float[rows_capacity]: routing weight of each padded row, 0 on padding rows */
     const int32_t* pos_MK;       /* int32[M*K]: padded row of token m's k-th expert (ascending expert id) */
     int32_t* status;             /* device int32 error word, zeroed by the caller */
+    const int32_t* pair_info;    /* int32[momoe_tile_capacity]: for each pair of consecutive tiles of one expert,
+                                    first tile * 2 + (1 if the pair has a second tile); the grouped GEMMs give one
+                                    pair to two cooperating thread blocks */
 } momoe_plan_t;
 
 int momoe_version(void);
@@ -76,9 +80,10 @@ int momoe_topk_from_mask(const int32_t* mask_NM, int64_t mask_stride_n, int64_t 
 size_t momoe_permutation_workspace_bytes(int32_t M, int32_t N, int32_t K);
 int momoe_build_permutation(const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N, int32_t K,
                             int64_t save_rows, int64_t* sizes_N, int32_t* cumsums_N1, int32_t* idx_Msum,
-                            int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert, int32_t* sched,
-                            int32_t* row_token, float* row_weight, int32_t* pos_MK, int64_t rows_capacity,
-                            void* workspace, size_t workspace_bytes, int32_t* status, momoe_stream_t stream);
+                            int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert, int32_t* pair_info,
+                            int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
+                            int64_t rows_capacity, void* workspace, size_t workspace_bytes, int32_t* status,
+                            momoe_stream_t stream);
 
 /* The same permutation builder for callers that cannot provide a workspace.  It has no counterpart in the
  * reference.  Some hosts of this library are not able to allocate device memory when they route tokens: an
@@ -96,8 +101,8 @@ int momoe_build_permutation(const int32_t* topk_idx_MK, const float* topk_w_MK, 
 int momoe_build_permutation_static(const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N,
                                    int32_t K, int64_t save_rows, int64_t* sizes_N, int32_t* cumsums_N1,
                                    int32_t* idx_Msum, int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert,
-                                   int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
-                                   int64_t rows_capacity, int32_t* status, momoe_stream_t stream);
+                                   int32_t* pair_info, int32_t* sched, int32_t* row_token, float* row_weight,
+                                   int32_t* pos_MK, int64_t rows_capacity, int32_t* status, momoe_stream_t stream);
 
 /* dst[r,:] = src[row_token[r],:] (zeros on padding rows), bf16, `cols` columns (multiple of 8).
  * Replaces the row gathers of momoe/momoe.py:116-118 and :298-350. */
@@ -128,7 +133,7 @@ int momoe_down_scale(const momoe_plan_t* plan, const void* h_sorted, const void*
  * gradient) and a,b taken from the saved buffers (tile < sched[1]) or the recomputed ones:
  *   gz_sorted [rows,2H] = bf16[ w*Gh*b*sig(b) | w*Gh*a*sig(b)*(1+b*(1-sig(b))) ]
  *   hs_sorted [rows,H]  = bf16( w * bf16(a*b*sig(b)) )           (left operand of the W2 gradient)
- *   gs_part   [rows,ceil(H/128)] fp32 partial sums of <Gh, bf16(a*b*sig(b))> (their sum is dL/ds). */
+ *   gs_part   [rows,2*ceil(H/256)] fp32 partial sums of <Gh, bf16(a*b*sig(b))> (their sum is dL/ds). */
 int momoe_dgrad2_swiglu_bwd(const momoe_plan_t* plan, const void* g_sorted, const void* W2_NHD,
                             const void* a_saved, const void* b_saved, const void* a_recomp, const void* b_recomp,
                             void* gz_sorted, void* hs_sorted, float* gs_part, momoe_stream_t stream);

@@ -1,17 +1,30 @@
-// Persistent grouped GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma (accumulators in TMEM) ->
-// epilogue warps.  One kernel template serves the five GEMMs of the MoMoE layer; they differ in operand
-// majorness, tile width and epilogue.
+// Persistent grouped GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma over a CTA PAIR (cta_group::2,
+// accumulators in TMEM) -> epilogue warps.  One kernel template serves the five GEMMs of the MoMoE layer; they
+// differ in operand majorness and epilogue.
 //
-// CTA = 192 threads: warp 0 (one lane) issues TMA loads, warp 1 allocates TMEM and (one lane) issues the MMAs,
-// warps 2..5 read accumulators out of TMEM (each warp owns the 32 TMEM lanes of its quarter, warp_id % 4) and
-// write the results.  Two accumulator buffers in TMEM let the epilogue of one tile overlap the main loop of
-// the next.  Every wait on an mbarrier is bounded (ptx.cuh); a wait that runs out records a code in the
-// caller's status word and every role leaves its loop.
+// Why CTA pairs: with one CTA per 128x256 tile the kernels were bound by the bytes an SM can take in through TMA
+// (48 KiB per 64-wide k-block against 512 MMA cycles); loads alone took 70 % of the kernel time.  A pair of CTAs on
+// two SMs computes a 256x256 tile: each CTA loads its own 128 rows of A and only HALF of B (32 KiB per k-block),
+// one thread of the leader CTA issues M=256 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives
+// its 128 rows x 256 columns.  Every TMA load has exactly one destination CTA.
+//
+// CTA = 320 threads: warp 0 (one lane) issues TMA loads, warp 1 allocates TMEM and (leader CTA, one lane) issues
+// the MMAs, warps 2..9 read accumulators out of TMEM and write the results.  A warp may only read the 32 TMEM lanes
+// of its quarter (warp_id % 4), so two warps share each quarter and split the tile's columns in halves.  Two
+// accumulator buffers in TMEM (2 x 256 columns) let the epilogue of one tile overlap the main loop of the next.
+//
+// Barriers (mbarrier in shared memory):
+//   full[s]      leader only; the leader's producer arms it with the bytes of BOTH CTAs, both CTAs' loads credit it
+//   empty[s]     one per CTA; the leader's tcgen05.commit arrives on both when the MMAs have read stage s
+//   acc_full[b]  one per CTA; commit arrives on both when the tile's last MMA has completed
+//   acc_empty[b] leader only; 16 arrivals = 8 epilogue warps of each CTA
+// Every wait is bounded (ptx.cuh); a wait that runs out records a code in the caller's status word and every role
+// leaves its loop; the CTAs still meet at the final cluster barrier and free TMEM.
 //
 // Shared-memory operand layouts (all 128-byte swizzled, as written by TMA with SWIZZLE_128B):
-//   K-major operand  [R rows x 64 k]: row r at byte r*128; descriptor SBO = 1024 (8-row group pitch);
+//   K-major operand  [128 rows x 64 k]: row r at byte r*128; descriptor SBO = 1024 (8-row group pitch);
 //                    one MMA (k = 16) advances the start address by 32 bytes.
-//   MN-major operand [64 k x 64 mn] boxes of 8 KiB: k-row at byte k*128, boxes along mn 8192 bytes apart;
+//   MN-major operand two [64 k x 64 mn] boxes of 8 KiB: k-row at byte k*128, boxes 8192 bytes apart;
 //                    descriptor LBO = 8192 (mn pitch), SBO = 1024 (8-k group pitch); one MMA advances 2048 bytes.
 #include <cstdio>
 #include <cstdlib>
@@ -23,17 +36,33 @@
 
 namespace momoe {
 
+constexpr int EPI_WARPS = 8;
+constexpr int CTA_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int PAIR_N = 256;                          // tile width of a CTA pair
+constexpr int A_BYTES = TILE_M * TILE_K * 2;         // 16 KiB: this CTA's 128 rows x 64 k
+constexpr int B_BYTES = (PAIR_N / 2) * TILE_K * 2;   // 16 KiB: this CTA's half of B x 64 k
+constexpr int HALF_BYTES = A_BYTES + B_BYTES;        // one 64-wide k slice
+// A pipeline stage holds TWO 64-wide k slices (k-block = 128): the barrier hand-shake per stage costs the issuing
+// thread about as many cycles as four MMAs take, so each hand-shake has to cover eight of them.
+constexpr int KB = 2 * TILE_K;
+constexpr int STAGE_BYTES = 2 * HALF_BYTES;
+constexpr int STAGES = 3;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
+constexpr int ACC_BUFS = 2;
+constexpr int TMEM_COLS = 512;
+
 enum GemmMode : int { MODE_UP = 0, MODE_DOWN = 1, MODE_DGRAD2 = 2, MODE_DGRAD1 = 3, MODE_WGRAD = 4 };
 
 struct GemmArgs {
     const int* sched;
     const int* tile_expert;
+    const int* pair_info;
     const int* pad_off;
     int* status;
     int n_experts;
-    int n_nblk;      // column blocks per row tile (row-tile modes) or per output row block (wgrad)
-    int n_mblk;      // wgrad: row blocks of one expert's output matrix
-    int nkb;         // row-tile modes: k-blocks of 64
+    int n_nblk;      // column blocks per row pair (row-tile modes) or per output row block (wgrad)
+    int n_mblk;      // wgrad: 256-row blocks of one expert's output matrix
+    int nkb;         // row-tile modes: k-blocks of 128
     int out_cols;    // valid output columns: H (up, dgrad2), D (down, dgrad1), Y (wgrad)
     int out_rows;    // wgrad: X
     int half;        // up: H, the column where the gate half of W1 starts
@@ -47,21 +76,19 @@ struct GemmArgs {
     const __nv_bfloat16* a_recomp;
     const __nv_bfloat16* b_recomp;
     float* gs_part;
-    uint32_t mn_lbo, mn_sbo;  // MN-major descriptor byte offsets
+    uint32_t dbg;    // debug builds only: bit 0 skip epilogue stores, bit 1 skip epilogue math, bit 2 skip MMA
 };
+
+#ifdef MOMOE_DEBUG_KNOBS
+#define DBG(g, bit) (((g).dbg >> (bit)) & 1u)
+#else
+#define DBG(g, bit) 0u
+#endif
 
 template <int MODE>
 struct Cfg {
     static constexpr bool A_MN = (MODE == MODE_WGRAD);
     static constexpr bool B_MN = (MODE == MODE_UP || MODE == MODE_DOWN || MODE == MODE_WGRAD);
-    static constexpr int BN = (MODE == MODE_DGRAD2) ? 128 : 256;
-    static constexpr int A_BYTES = TILE_M * TILE_K * 2;   // 16 KiB
-    static constexpr int B_BYTES = BN * TILE_K * 2;       // 16 or 32 KiB
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : 6;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
-    static constexpr int ACC_BUFS = 2;
-    static constexpr int TMEM_COLS = 512;
 };
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -73,7 +100,7 @@ __device__ __forceinline__ void unpack_bf16(uint32_t v, float& lo, float& hi) {
     lo = __uint_as_float(v << 16);
     hi = __uint_as_float(v & 0xFFFF0000u);
 }
-__device__ __forceinline__ float sigmoidf_fast(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 // Store 32 consecutive fp32 values as bf16 to dst (16-byte aligned), keeping only columns < ncols_left.
 // ncols_left is a multiple of 8 by contract (all matrix widths are).
@@ -90,6 +117,32 @@ __device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float (&v)
         }
     }
 }
+// 256-bit global accesses (one full 32-byte sector per thread): half as many load/store instructions, which
+// matters because the row-per-thread pattern of the epilogues costs one tag look-up per thread and instruction.
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void ld_global_nc_256(const void* p, uint32_t (&v)[8]) {
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "l"(p));
+}
+// Same as store_row32 for rows whose pitch is a multiple of 32 bytes and a fully valid 32-column chunk.
+__device__ __forceinline__ void store_row32_wide(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        uint32_t q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = pack_bf16(v[g * 16 + 2 * j], v[g * 16 + 2 * j + 1]);
+        st_global_256(dst + g * 16, q);
+    }
+}
+__device__ __forceinline__ void store_row32_auto(__nv_bfloat16* dst, const float (&v)[32], int ncols_left, bool wide) {
+    if (wide && ncols_left >= 32) store_row32_wide(dst, v);
+    else store_row32(dst, v, ncols_left);
+}
 // Load 32 consecutive bf16 values (16-byte aligned) as fp32; columns >= ncols_left read as zero.
 __device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float (&v)[32], int ncols_left) {
 #pragma unroll
@@ -103,19 +156,24 @@ __device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float (&v)[
     }
 }
 
-// Work item -> coordinates.  Row-tile modes: item = tile * n_nblk + nb.  Wgrad: item = (e * n_mblk + mb) * n_nblk + nb.
+// Work item -> coordinates of THIS CTA.
+// Row-tile modes: item = pair * n_nblk + nb; a pair is two consecutive 128-row tiles of one expert (the second may be
+// missing when the expert has an odd number of tiles).  Wgrad: item = (e * n_mblk + mb) * n_nblk + nb.
 struct Work {
-    int tile;   // row tile (row-tile modes)
-    int e;      // expert
-    int mb;     // wgrad: output row block
-    int nb;     // column block
-    int nkb;    // k-blocks
-    int row0;   // wgrad: first padded row of the expert
+    int tile;    // this CTA's row tile (row-tile modes)
+    int e;       // expert
+    int mb;      // wgrad: 256-row output block
+    int nb;      // column block
+    int nkb;     // k-blocks
+    int row0;    // wgrad: first padded row of the expert
+    bool valid;  // this CTA's half of the pair holds real work
+    bool skip;   // up/recompute: every tile of the pair is saved, nothing to do (same answer in both CTAs)
 };
 
 template <int MODE>
-__device__ __forceinline__ Work decode_work(const GemmArgs& g, int item, int first_tile) {
+__device__ __forceinline__ Work decode_work(const GemmArgs& g, int item, uint32_t cta_rank) {
     Work w;
+    w.skip = false;
     if constexpr (MODE == MODE_WGRAD) {
         w.nb = item % g.n_nblk;
         const int t = item / g.n_nblk;
@@ -123,49 +181,56 @@ __device__ __forceinline__ Work decode_work(const GemmArgs& g, int item, int fir
         w.e = t / g.n_mblk;
         w.tile = 0;
         w.row0 = __ldg(g.pad_off + w.e);
-        w.nkb = (__ldg(g.pad_off + w.e + 1) - w.row0) / TILE_K;
+        w.nkb = (__ldg(g.pad_off + w.e + 1) - w.row0) / KB;   // padded rows are a multiple of 128
+        w.valid = true;
     } else {
         w.nb = item % g.n_nblk;
-        w.tile = first_tile + item / g.n_nblk;
-        w.e = __ldg(g.tile_expert + w.tile);
+        const int info = __ldg(g.pair_info + item / g.n_nblk);
+        const int t0 = info >> 1;
+        const int has2 = info & 1;
+        w.tile = t0 + static_cast<int>(cta_rank);
+        w.valid = cta_rank == 0 || has2 != 0;
+        w.e = __ldg(g.tile_expert + t0);
         w.mb = 0;
         w.nkb = g.nkb;
         w.row0 = 0;
+        if (MODE == MODE_UP && g.ab_mode == 2) w.skip = (t0 + has2) < __ldg(g.sched + SCHED_N_SAVED_TILES);
     }
     return w;
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmArgs g) {
     using C = Cfg<MODE>;
-    constexpr int BN = C::BN;
-    constexpr int STAGES = C::STAGES;
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[STAGES];
     __shared__ uint64_t bar_empty[STAGES];
-    __shared__ uint64_t bar_acc_full[C::ACC_BUFS];
-    __shared__ uint64_t bar_acc_empty[C::ACC_BUFS];
+    __shared__ uint64_t bar_acc_full[ACC_BUFS];
+    __shared__ uint64_t bar_acc_empty[ACC_BUFS];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();
+    const bool leader = cta_rank == 0;
+    const int cluster_id = blockIdx.x >> 1;
+    const int n_clusters = gridDim.x >> 1;
     const uint32_t stage_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+#ifdef MOMOE_DEBUG_KNOBS
+    long long dbg_c0 = clock64();
+    unsigned long long dbg_t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(dbg_t0));
+#endif
 
     // ---- work range (device-resident schedule; nothing is read back by the host)
-    int first_tile = 0;
     int total_items;
-    if constexpr (MODE == MODE_WGRAD) {
-        total_items = g.n_experts * g.n_mblk * g.n_nblk;
-    } else {
-        const int n_tiles = __ldg(g.sched + SCHED_N_TILES);
-        if (MODE == MODE_UP && g.ab_mode == 2) first_tile = __ldg(g.sched + SCHED_N_SAVED_TILES);
-        total_items = (n_tiles - first_tile) * g.n_nblk;
-    }
-    if (total_items <= 0 || static_cast<int>(blockIdx.x) >= total_items) return;  // whole CTA leaves together
+    if constexpr (MODE == MODE_WGRAD) total_items = g.n_experts * g.n_mblk * g.n_nblk;
+    else total_items = __ldg(g.sched + SCHED_N_PAIRS) * g.n_nblk;
+    if (total_items <= 0 || cluster_id >= total_items) return;  // both CTAs of the cluster leave together
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -173,63 +238,76 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
-        for (int b = 0; b < C::ACC_BUFS; ++b) {
+        for (int b = 0; b < ACC_BUFS; ++b) {
             mbar_init(smem_u32(&bar_acc_full[b]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[b]), 4);  // one arrival per epilogue warp
+            mbar_init(smem_u32(&bar_acc_empty[b]), 2 * EPI_WARPS);  // one arrival per epilogue warp of both CTAs
         }
         fence_mbar_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(&tmem_slot), C::TMEM_COLS);
-        tmem_relinquish();
+        tmem_alloc_pair(smem_u32(&tmem_slot), TMEM_COLS);
+        tmem_relinquish_pair();
     }
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();   // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
     volatile int* abortp = &abort_flag;
 
     if (warp == 0) {
-        // ================================================================ TMA producer
+        // ================================================================ TMA producer (both CTAs)
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-                const Work w = decode_work<MODE>(g, item, first_tile);
+            for (int item = cluster_id; ok && item < total_items; item += n_clusters) {
+                const Work w = decode_work<MODE>(g, item, cta_rank);
+                if (w.skip) continue;
                 for (int kb = 0; kb < w.nkb; ++kb) {
                     ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, g.status, DEV_TIMEOUT_PRODUCER);
                     if (!ok) break;
-                    const uint32_t sa = stage_base + stage * C::STAGE_BYTES;
-                    const uint32_t sb = sa + C::A_BYTES;
-                    const uint32_t full = smem_u32(&bar_full[stage]);
-                    mbar_arrive_expect_tx(full, C::STAGE_BYTES);
-                    if constexpr (MODE == MODE_WGRAD) {
-                        const int r0 = w.row0 + kb * TILE_K;
+                    if (DBG(g, 4)) {   // debug: no loads at all, the MMAs run on whatever shared memory holds
+                        if (leader) mbar_arrive(smem_u32(&bar_full[stage]));
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
+                    if (leader) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2 * STAGE_BYTES);
+                    const uint32_t full = mapa_shared(smem_u32(&bar_full[stage]), 0);   // the leader's barrier
+                    const int r = static_cast<int>(cta_rank);
+                    // two 64-wide k slices; a slice past the end of the k axis is zero-filled by TMA
 #pragma unroll
-                        for (int i = 0; i < TILE_M / 64; ++i)
-                            tma_load_2d(sa + i * 8192, &tmA, full, w.mb * TILE_M + i * 64, r0);
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t sa = stage_base + stage * STAGE_BYTES + h * HALF_BYTES;
+                        const uint32_t sb = sa + A_BYTES;
+                        const int k0 = kb * KB + h * TILE_K;
+                        if constexpr (MODE == MODE_WGRAD) {
+                            const int r0 = w.row0 + k0;
 #pragma unroll
-                        for (int i = 0; i < BN / 64; ++i)
-                            tma_load_2d(sb + i * 8192, &tmB, full, w.nb * BN + i * 64, r0);
-                    } else {
-                        tma_load_2d(sa, &tmA, full, kb * TILE_K, w.tile * TILE_M);
-                        if constexpr (MODE == MODE_UP) {
-                            // 4 boxes of 64 columns: two from the linear half, two from the gate half of W1[e]
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int col = (i < 2 ? 0 : g.half) + w.nb * 128 + (i & 1) * 64;
-                                tma_load_3d(sb + i * 8192, &tmB, full, col, kb * TILE_K, w.e);
+                            for (int i = 0; i < 2; ++i) {
+                                tma_load_2d_pair(sa + i * 8192, &tmA, full, w.mb * 256 + r * 128 + i * 64, r0);
+                                tma_load_2d_pair(sb + i * 8192, &tmB, full, w.nb * PAIR_N + r * 128 + i * 64, r0);
                             }
-                        } else if constexpr (MODE == MODE_DOWN) {
-#pragma unroll
-                            for (int i = 0; i < BN / 64; ++i)
-                                tma_load_3d(sb + i * 8192, &tmB, full, w.nb * BN + i * 64, kb * TILE_K, w.e);
                         } else {
-                            // K-major weights: rows = output columns, 64 contiguous k per row
-                            tma_load_3d(sb, &tmB, full, kb * TILE_K, w.nb * BN, w.e);
+                            tma_load_2d_pair(sa, &tmA, full, k0, w.tile * TILE_M);
+                            if constexpr (MODE == MODE_UP) {
+                                // the leader loads 128 columns of the linear half of W1[e], its peer the matching
+                                // 128 columns of the gate half: accumulator columns 0..127 = a, 128..255 = b
+#pragma unroll
+                                for (int i = 0; i < 2; ++i)
+                                    tma_load_3d_pair(sb + i * 8192, &tmB, full, r * g.half + w.nb * 128 + i * 64, k0,
+                                                     w.e);
+                            } else if constexpr (MODE == MODE_DOWN) {
+#pragma unroll
+                                for (int i = 0; i < 2; ++i)
+                                    tma_load_3d_pair(sb + i * 8192, &tmB, full, w.nb * PAIR_N + r * 128 + i * 64, k0,
+                                                     w.e);
+                            } else {
+                                // K-major weights: rows = output columns, 64 contiguous k per row
+                                tma_load_3d_pair(sb, &tmB, full, k0, w.nb * PAIR_N + r * 128, w.e);
+                            }
                         }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -237,148 +315,254 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
         }
     } else if (warp == 1) {
-        // ================================================================ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN, C::A_MN, C::B_MN);
+        // ================================================================ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = umma_idesc_bf16(2 * TILE_M, PAIR_N, C::A_MN, C::B_MN);
+            // Descriptor halves.  High half (constant): SBO = 1024 >> 4, version 1 (bit 46), 128-byte swizzle
+            // (bits 61..63).  Low half: start address >> 4 in [0,14), LBO >> 4 in [16,30).  Only the start address
+            // changes from MMA to MMA, so the loop below is a handful of 32-bit adds per MMA.
+            constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            constexpr uint32_t a_lbo = C::A_MN ? (8192u >> 4) : 1u;
+            constexpr uint32_t b_lbo = C::B_MN ? (8192u >> 4) : 1u;
+            constexpr uint32_t a_kstep = C::A_MN ? (2048u >> 4) : (32u >> 4);   // per 16-wide k step
+            constexpr uint32_t b_kstep = C::B_MN ? (2048u >> 4) : (32u >> 4);
+            const uint32_t a_lo0 = ((stage_base >> 4) & 0x3FFFu) | (a_lbo << 16);
+            const uint32_t b_lo0 = (((stage_base + A_BYTES) >> 4) & 0x3FFFu) | (b_lbo << 16);
             int stage = 0;
             uint32_t phase = 0;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;
             int it = 0;
             bool ok = true;
-            for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
-                const Work w = decode_work<MODE>(g, item, first_tile);
+            for (int item = cluster_id; ok && item < total_items; item += n_clusters) {
+                const Work w = decode_work<MODE>(g, item, cta_rank);
+                if (w.skip) continue;
                 const int ab = it & 1;
                 const uint32_t aphase = (it >> 1) & 1u;
+                ++it;
                 ok = mbar_wait(smem_u32(&bar_acc_empty[ab]), aphase ^ 1u, abortp, g.status, DEV_TIMEOUT_MMA);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + ab * BN;
+                const uint32_t tmem_d = tmem_base + ab * PAIR_N;
                 for (int kb = 0; kb < w.nkb; ++kb) {
                     ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, g.status, DEV_TIMEOUT_MMA);
                     if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t sa = stage_base + stage * C::STAGE_BYTES;
-                    const uint32_t sb = sa + C::A_BYTES;
+                    if (!DBG(g, 2)) {
+                        umma_bf16_pair_lohi(tmem_d, a_lo, desc_hi, b_lo, desc_hi, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-                        const uint64_t da = C::A_MN ? umma_smem_desc(sa + k * 2048, g.mn_lbo, g.mn_sbo)
-                                                    : umma_smem_desc(sa + k * 32, 16, 1024);
-                        const uint64_t db = C::B_MN ? umma_smem_desc(sb + k * 2048, g.mn_lbo, g.mn_sbo)
-                                                    : umma_smem_desc(sb + k * 32, 16, 1024);
-                        umma_bf16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                        for (uint32_t k = 1; k < (DBG(g, 6) ? 1u : 2u * TILE_K / UMMA_K); ++k) {
+                            const uint32_t off = (k >> 2) * (HALF_BYTES >> 4);   // second 64-wide slice of the stage
+                            umma_bf16_pair_lohi(tmem_d, a_lo + off + (k & 3u) * a_kstep, desc_hi,
+                                                b_lo + off + (k & 3u) * b_kstep, desc_hi, idesc, 1u);
+                        }
                     }
-                    umma_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    umma_commit_pair(smem_u32(&bar_empty[stage]), 3);  // frees the stage in both CTAs
+                    a_lo += STAGE_BYTES >> 4;
+                    b_lo += STAGE_BYTES >> 4;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
                 }
                 if (!ok) break;
-                if (w.nkb > 0) umma_commit(smem_u32(&bar_acc_full[ab]));
-                else mbar_arrive(smem_u32(&bar_acc_full[ab]));  // nothing to accumulate: epilogue writes zeros
+                if (w.nkb > 0) {
+                    umma_commit_pair(smem_u32(&bar_acc_full[ab]), 3);
+                } else {
+                    // nothing to accumulate (expert without tokens): wake both epilogues, they write zeros
+                    mbar_arrive(smem_u32(&bar_acc_full[ab]));
+                    mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_full[ab]), 1));
+                }
             }
         }
     } else {
-        // ================================================================ epilogue (warps 2..5)
+        // ================================================================ epilogue (warps 2..9, both CTAs)
         const int q = warp & 3;            // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;     // accumulator row == TMEM lane
+        const int half = (warp - 2) >> 2;  // which half of the tile's 32-column chunks this warp handles
+        const uint32_t acc_empty_leader = mapa_shared(smem_u32(&bar_acc_empty[0]), 0);
+        const bool wide = (g.out_cols % 16) == 0;   // every row of the outputs starts on a 32-byte boundary
         int it = 0;
         bool ok = true;
-        for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++it) {
-            const Work w = decode_work<MODE>(g, item, first_tile);
+        for (int item = cluster_id; ok && item < total_items; item += n_clusters) {
+            const Work w = decode_work<MODE>(g, item, cta_rank);
+            if (w.skip) continue;
             const int ab = it & 1;
             const uint32_t aphase = (it >> 1) & 1u;
+            ++it;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * PAIR_N;
+            uint32_t r[32];
+            if constexpr (MODE == MODE_DGRAD2) {
+                // The saved / recomputed a,b rows do not depend on the accumulator: the first 32-column chunk is
+                // fetched while the main loop is still running, each later chunk while the previous one is computed.
+                const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
+                const int H = g.out_cols;
+                const int n_saved = __ldg(g.sched + SCHED_N_SAVED_TILES);
+                const bool saved = w.tile < n_saved;
+                const size_t abrow =
+                    (saved ? static_cast<size_t>(w.tile) : static_cast<size_t>(w.tile - n_saved)) * TILE_M + row;
+                const __nv_bfloat16* ap = (saved ? g.a_saved : g.a_recomp) + abrow * H;
+                const __nv_bfloat16* bp = (saved ? g.b_saved : g.b_recomp) + abrow * H;
+                const int c_begin = half * 4, c_end = half * 4 + 4;
+                uint4 na[4], nb4[4];
+                auto fetch = [&](int c) {
+                    const int col0 = w.nb * PAIR_N + c * 32;
+                    if (wide && w.valid && col0 + 32 <= H) {
+                        uint32_t t[8];
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            ld_global_nc_256(ap + col0 + i * 16, t);
+                            na[2 * i] = make_uint4(t[0], t[1], t[2], t[3]);
+                            na[2 * i + 1] = make_uint4(t[4], t[5], t[6], t[7]);
+                            ld_global_nc_256(bp + col0 + i * 16, t);
+                            nb4[2 * i] = make_uint4(t[0], t[1], t[2], t[3]);
+                            nb4[2 * i + 1] = make_uint4(t[4], t[5], t[6], t[7]);
+                        }
+                        return;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const bool in = w.valid && col0 + i * 8 < H;
+                        na[i] = in ? __ldg(reinterpret_cast<const uint4*>(ap + col0 + i * 8)) : make_uint4(0, 0, 0, 0);
+                        nb4[i] = in ? __ldg(reinterpret_cast<const uint4*>(bp + col0 + i * 8)) : make_uint4(0, 0, 0, 0);
+                    }
+                };
+                fetch(c_begin);
+                const float wgt = w.valid ? __ldg(g.row_weight + grow) : 0.0f;
+                ok = mbar_wait(smem_u32(&bar_acc_full[ab]), aphase, abortp, g.status, DEV_TIMEOUT_EPILOGUE);
+                if (!ok) break;
+                tc_fence_after();
+                if (w.valid) {
+                    float gs = 0.0f;
+#pragma unroll 1
+                    for (int c = c_begin; c < c_end; ++c) {
+                        const int col0 = w.nb * PAIR_N + c * 32;
+                        const int left = H - col0;
+                        if (left <= 0) break;
+                        uint4 ca[4], cb[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { ca[i] = na[i]; cb[i] = nb4[i]; }
+                        if (c + 1 < c_end) fetch(c + 1);
+                        tmem_ld32(taddr + c * 32, r);
+                        tmem_ld_wait();
+                        __nv_bfloat16* z1p = g.out0 + grow * (2 * H) + col0;
+                        __nv_bfloat16* hsp = g.out1 + grow * H + col0;
+#pragma unroll
+                        for (int i2 = 0; i2 < 2; ++i2) {   // 16 columns at a time: compute, pack, store
+                            uint32_t o1[8], o2[8], o3[8];
+#pragma unroll
+                            for (int ii = 0; ii < 2; ++ii) {
+                                const int i = i2 * 2 + ii;
+                                const uint32_t pa[4] = {ca[i].x, ca[i].y, ca[i].z, ca[i].w};
+                                const uint32_t pb[4] = {cb[i].x, cb[i].y, cb[i].z, cb[i].w};
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float a0, a1, b0, b1;
+                                    unpack_bf16(pa[j], a0, a1);
+                                    unpack_bf16(pb[j], b0, b1);
+                                    const float g0 = __uint_as_float(r[i * 8 + 2 * j]);
+                                    const float g1 = __uint_as_float(r[i * 8 + 2 * j + 1]);
+                                    const float s0 = sigmoidf_fast(b0), s1 = sigmoidf_fast(b1);
+                                    const float h0 = bf16_round(a0 * b0 * s0), h1 = bf16_round(a1 * b1 * s1);
+                                    gs = fmaf(g0, h0, gs);
+                                    gs = fmaf(g1, h1, gs);
+                                    const float gh0 = wgt * g0, gh1 = wgt * g1;
+                                    o1[ii * 4 + j] = pack_bf16(gh0 * b0 * s0, gh1 * b1 * s1);
+                                    o2[ii * 4 + j] = pack_bf16(gh0 * a0 * s0 * fmaf(b0, 1.0f - s0, 1.0f),
+                                                               gh1 * a1 * s1 * fmaf(b1, 1.0f - s1, 1.0f));   // gate half
+                                    o3[ii * 4 + j] = pack_bf16(wgt * h0, wgt * h1);
+                                }
+                            }
+                            if (DBG(g, 0)) continue;
+                            if (wide && left >= 32) {
+                                st_global_256(z1p + i2 * 16, o1);
+                                st_global_256(z1p + H + i2 * 16, o2);
+                                st_global_256(hsp + i2 * 16, o3);
+                            } else {
+#pragma unroll
+                                for (int ii = 0; ii < 2; ++ii) {
+                                    const int i = i2 * 2 + ii;
+                                    if (i * 8 < left) {
+                                        *reinterpret_cast<uint4*>(z1p + i * 8) =
+                                            make_uint4(o1[ii * 4], o1[ii * 4 + 1], o1[ii * 4 + 2], o1[ii * 4 + 3]);
+                                        *reinterpret_cast<uint4*>(z1p + H + i * 8) =
+                                            make_uint4(o2[ii * 4], o2[ii * 4 + 1], o2[ii * 4 + 2], o2[ii * 4 + 3]);
+                                        *reinterpret_cast<uint4*>(hsp + i * 8) =
+                                            make_uint4(o3[ii * 4], o3[ii * 4 + 1], o3[ii * 4 + 2], o3[ii * 4 + 3]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    g.gs_part[(grow * g.n_nblk + w.nb) * 2 + half] = gs;   // two partial sums per 256-column block
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+                    else mbar_arrive_cluster(acc_empty_leader + ab * static_cast<uint32_t>(sizeof(uint64_t)));
+                }
+                continue;
+            }
             ok = mbar_wait(smem_u32(&bar_acc_full[ab]), aphase, abortp, g.status, DEV_TIMEOUT_EPILOGUE);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN;
-            uint32_t r[32];
             float v[32];
 
-            if constexpr (MODE == MODE_UP) {
+            if (DBG(g, 5)) {
+                // debug: handshake only
+            } else if constexpr (MODE == MODE_UP) {
                 const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
                 const int n_saved = __ldg(g.sched + SCHED_N_SAVED_TILES);
-                const bool store_ab = (g.ab_mode == 1 && w.tile < n_saved) || g.ab_mode == 2;
+                const bool store_ab = (g.ab_mode == 1 && w.tile < n_saved) || (g.ab_mode == 2 && w.tile >= n_saved);
                 const size_t abrow =
                     (g.ab_mode == 2 ? static_cast<size_t>(w.tile - n_saved) : static_cast<size_t>(w.tile)) * TILE_M + row;
+                if (w.valid) {
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    const int col0 = w.nb * 128 + c * 32;
-                    const int left = g.out_cols - col0;
-                    if (left <= 0) break;   // uniform across the warp
-                    float a[32], b[32];
-                    tmem_ld32(taddr + c * 32, r);
-                    tmem_ld_wait();
+                    for (int c = half * 2; c < half * 2 + 2; ++c) {
+                        const int col0 = w.nb * 128 + c * 32;
+                        const int left = g.out_cols - col0;
+                        if (left <= 0) break;   // uniform across the warp
+                        float a[32], b[32];
+                        tmem_ld32(taddr + c * 32, r);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) a[i] = __uint_as_float(r[i]);
-                    tmem_ld32(taddr + 128 + c * 32, r);
-                    tmem_ld_wait();
+                        for (int i = 0; i < 32; ++i) a[i] = __uint_as_float(r[i]);
+                        tmem_ld32(taddr + 128 + c * 32, r);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) b[i] = __uint_as_float(r[i]);
-                    if (store_ab) {
-                        store_row32(g.out1 + abrow * g.out_cols + col0, a, left);
-                        store_row32(g.out2 + abrow * g.out_cols + col0, b, left);
-                    }
-                    if (g.out0 != nullptr) {
+                        for (int i = 0; i < 32; ++i) b[i] = __uint_as_float(r[i]);
+                        if (store_ab) {
+                            store_row32_auto(g.out1 + abrow * g.out_cols + col0, a, DBG(g, 0) ? 0 : left, wide);
+                            store_row32_auto(g.out2 + abrow * g.out_cols + col0, b, DBG(g, 0) ? 0 : left, wide);
+                        }
+                        if (g.out0 != nullptr) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = b[i] * sigmoidf_fast(b[i]) * a[i];
-                        store_row32(g.out0 + grow * g.out_cols + col0, v, left);
+                            for (int i = 0; i < 32; ++i) v[i] = b[i] * sigmoidf_fast(b[i]) * a[i];
+                            store_row32_auto(g.out0 + grow * g.out_cols + col0, v, DBG(g, 0) ? 0 : left, wide);
+                        }
                     }
                 }
             } else if constexpr (MODE == MODE_DOWN || MODE == MODE_DGRAD1) {
                 const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
-                float wgt = 1.0f;
-                if constexpr (MODE == MODE_DOWN) wgt = __ldg(g.row_weight + grow);
+                if (w.valid) {
+                    float wgt = 1.0f;
+                    if constexpr (MODE == MODE_DOWN) wgt = __ldg(g.row_weight + grow);
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    const int col0 = w.nb * BN + c * 32;
-                    const int left = g.out_cols - col0;
-                    if (left <= 0) break;
-                    tmem_ld32(taddr + c * 32, r);
-                    tmem_ld_wait();
+                    for (int c = half * 4; c < half * 4 + 4; ++c) {
+                        const int col0 = w.nb * PAIR_N + c * 32;
+                        const int left = g.out_cols - col0;
+                        if (left <= 0) break;
+                        tmem_ld32(taddr + c * 32, r);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * wgt;
-                    store_row32(g.out0 + grow * g.out_cols + col0, v, left);
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * wgt;
+                        store_row32_auto(g.out0 + grow * g.out_cols + col0, v, DBG(g, 0) ? 0 : left, wide);
+                    }
                 }
             } else if constexpr (MODE == MODE_DGRAD2) {
-                const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
-                const int n_saved = __ldg(g.sched + SCHED_N_SAVED_TILES);
-                const bool saved = w.tile < n_saved;
-                const size_t abrow = (saved ? static_cast<size_t>(w.tile) : static_cast<size_t>(w.tile - n_saved)) * TILE_M + row;
-                const __nv_bfloat16* ap = (saved ? g.a_saved : g.a_recomp) + abrow * g.out_cols;
-                const __nv_bfloat16* bp = (saved ? g.b_saved : g.b_recomp) + abrow * g.out_cols;
-                const float wgt = __ldg(g.row_weight + grow);
-                const int H = g.out_cols;
-                float gs = 0.0f;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    const int col0 = w.nb * BN + c * 32;
-                    const int left = H - col0;
-                    if (left <= 0) break;
-                    float a[32], b[32];
-                    load_row32(ap + col0, a, left);
-                    load_row32(bp + col0, b, left);
-                    tmem_ld32(taddr + c * 32, r);
-                    tmem_ld_wait();
-                    float z1[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float gh_raw = __uint_as_float(r[i]);
-                        const float sg = sigmoidf_fast(b[i]);
-                        const float hh = bf16_round(a[i] * b[i] * sg);
-                        gs += gh_raw * hh;
-                        const float gh = wgt * gh_raw;
-                        z1[i] = gh * b[i] * sg;
-                        v[i] = gh * a[i] * sg * (1.0f + b[i] * (1.0f - sg));   // gate-half gradient
-                        a[i] = wgt * hh;                                        // reuse a[] for hs
-                    }
-                    store_row32(g.out0 + grow * (2 * H) + col0, z1, left);
-                    store_row32(g.out0 + grow * (2 * H) + H + col0, v, left);
-                    store_row32(g.out1 + grow * H + col0, a, left);
-                }
-                g.gs_part[grow * g.n_nblk + w.nb] = gs;
+                // handled below: its operand prefetch starts before the accumulator wait
             } else {  // MODE_WGRAD
-                const int orow = w.mb * TILE_M + row;
+                const int orow = w.mb * 256 + static_cast<int>(cta_rank) * TILE_M + row;
                 __nv_bfloat16* dst = g.out0 + (static_cast<size_t>(w.e) * g.out_rows + orow) * g.out_cols;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    const int col0 = w.nb * BN + c * 32;
+                for (int c = half * 4; c < half * 4 + 4; ++c) {
+                    const int col0 = w.nb * PAIR_N + c * 32;
                     const int left = g.out_cols - col0;
                     if (left <= 0) break;
                     if (w.nkb > 0) {
@@ -390,35 +574,47 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                     }
-                    if (orow < g.out_rows) store_row32(dst + col0, v, left);
+                    if (orow < g.out_rows) store_row32_auto(dst + col0, v, DBG(g, 0) ? 0 : left, wide);
                 }
             }
-            // hand the accumulator buffer back to the MMA warp
+            // hand the accumulator buffer back to the MMA thread of the leader CTA
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+            if (lane == 0) {
+                if (leader) mbar_arrive(smem_u32(&bar_acc_empty[ab]));
+                else mbar_arrive_cluster(acc_empty_leader + ab * static_cast<uint32_t>(sizeof(uint64_t)));
+            }
         }
     }
 
-    // ---- teardown: everybody meets, then the allocating warp frees TMEM
+    // ---- teardown: both CTAs meet (the peer's shared memory and TMEM stay alive until the leader's last MMA has
+    // been consumed), then the allocating warps free TMEM
     tc_fence_before();
     __syncthreads();
     if (*abortp) {
         // a wait was abandoned: give loads still in flight time to land before shared memory is released
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) __nanosleep(1000);
-        __syncthreads();
     }
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, C::TMEM_COLS);
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
+#ifdef MOMOE_DEBUG_KNOBS
+    if (DBG(g, 3) && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        const long long dc = clock64() - dbg_c0;
+        printf("mode %d: %lld cycles in %llu ns = %.0f MHz\n", MODE, dc, t1 - dbg_t0, 1e3 * dc / double(t1 - dbg_t0));
+    }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------- host side
 static int check_plan(const momoe_plan_t* p) {
     if (p == nullptr || p->sched == nullptr || p->tile_expert == nullptr || p->pad_off == nullptr ||
-        p->row_weight == nullptr || p->status == nullptr)
+        p->row_weight == nullptr || p->status == nullptr || p->pair_info == nullptr)
         return MOMOE_ERR_ARG;
     if (p->M <= 0 || p->N <= 0 || p->K <= 0 || p->D <= 0 || p->H <= 0 || p->rows_capacity <= 0) return MOMOE_ERR_ARG;
     if (p->D % 8 != 0 || p->H % 8 != 0) return MOMOE_ERR_UNSUPPORTED;  // TMA row pitch must be a multiple of 16 bytes
@@ -430,29 +626,54 @@ static void base_args(const momoe_plan_t* p, GemmArgs& g) {
     memset(&g, 0, sizeof(g));
     g.sched = p->sched;
     g.tile_expert = p->tile_expert;
+    g.pair_info = p->pair_info;
     g.pad_off = p->pad_off;
     g.status = p->status;
     g.n_experts = p->N;
     g.row_weight = p->row_weight;
-    g.mn_lbo = 8192;
-    g.mn_sbo = 1024;
 #ifdef MOMOE_DEBUG_KNOBS
-    if (const char* s = getenv("MOMOE_DEBUG_MN_DESC")) {
-        unsigned a = 0, b = 0;
-        if (sscanf(s, "%u,%u", &a, &b) == 2) { g.mn_lbo = a; g.mn_sbo = b; }
-    }
+    if (const char* s = getenv("MOMOE_DEBUG_FLAGS")) g.dbg = static_cast<uint32_t>(atoi(s));
 #endif
+}
+
+// Number of CTA pairs that can be resident at once (the two CTAs of a pair sit on neighbouring SMs).
+template <int MODE>
+static int resident_pairs() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return sm_count() / 2;
+    if (cached[dev] == 0) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(static_cast<unsigned>(sm_count() / 2 * 2));
+        cfg.blockDim = dim3(CTA_THREADS);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, grouped_gemm_kernel<MODE>, &cfg) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = sm_count() / 2;
+        }
+        if (n > sm_count() / 2) n = sm_count() / 2;
+        cached[dev] = n;
+    }
+    return cached[dev];
 }
 
 template <int MODE>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, cudaStream_t stream) {
-    using C = Cfg<MODE>;
     // per-device attribute; setting it on every launch costs well under a microsecond of host time
-    if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             C::SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess)
         return MOMOE_ERR_CUDA;
-    const int grid = sm_count();
-    grouped_gemm_kernel<MODE><<<grid, 192, C::SMEM_BYTES, stream>>>(tmA, tmB, g);
+    const int grid = 2 * resident_pairs<MODE>();
+    grouped_gemm_kernel<MODE><<<grid, CTA_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, g);
     return cudaGetLastError() == cudaSuccess ? MOMOE_OK : MOMOE_ERR_CUDA;
 }
 
@@ -462,8 +683,10 @@ static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
 using namespace momoe;
 
-extern "C" __attribute__((visibility("default"))) int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted, const void* W1_ND2H, void* h_sorted,
-                               void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream) {
+extern "C" __attribute__((visibility("default"))) int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted,
+                                                                     const void* W1_ND2H, void* h_sorted, void* a_out,
+                                                                     void* b_out, int32_t ab_mode,
+                                                                     momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
     if (x_sorted == nullptr || W1_ND2H == nullptr) return MOMOE_ERR_ARG;
@@ -477,7 +700,7 @@ extern "C" __attribute__((visibility("default"))) int momoe_up_swiglu(const momo
     GemmArgs g;
     base_args(plan, g);
     g.n_nblk = cdiv(H, 128);
-    g.nkb = cdiv(D, TILE_K);
+    g.nkb = cdiv(D, KB);
     g.out_cols = H;
     g.half = H;
     g.ab_mode = ab_mode;
@@ -487,8 +710,9 @@ extern "C" __attribute__((visibility("default"))) int momoe_up_swiglu(const momo
     return launch<MODE_UP>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" __attribute__((visibility("default"))) int momoe_down_scale(const momoe_plan_t* plan, const void* h_sorted, const void* W2_NHD, void* y_sorted,
-                                momoe_stream_t stream) {
+extern "C" __attribute__((visibility("default"))) int momoe_down_scale(const momoe_plan_t* plan, const void* h_sorted,
+                                                                      const void* W2_NHD, void* y_sorted,
+                                                                      momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
     if (h_sorted == nullptr || W2_NHD == nullptr || y_sorted == nullptr) return MOMOE_ERR_ARG;
@@ -498,17 +722,17 @@ extern "C" __attribute__((visibility("default"))) int momoe_down_scale(const mom
     if ((rc = encode_tmap_3d(&tmB, W2_NHD, plan->N, H, D, TILE_K, 64)) != MOMOE_OK) return rc;
     GemmArgs g;
     base_args(plan, g);
-    g.n_nblk = cdiv(D, 256);
-    g.nkb = cdiv(H, TILE_K);
+    g.n_nblk = cdiv(D, PAIR_N);
+    g.nkb = cdiv(H, KB);
     g.out_cols = D;
     g.out0 = static_cast<__nv_bfloat16*>(y_sorted);
     return launch<MODE_DOWN>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" __attribute__((visibility("default"))) int momoe_dgrad2_swiglu_bwd(const momoe_plan_t* plan, const void* g_sorted, const void* W2_NHD,
-                                       const void* a_saved, const void* b_saved, const void* a_recomp,
-                                       const void* b_recomp, void* gz_sorted, void* hs_sorted, float* gs_part,
-                                       momoe_stream_t stream) {
+extern "C" __attribute__((visibility("default"))) int momoe_dgrad2_swiglu_bwd(
+    const momoe_plan_t* plan, const void* g_sorted, const void* W2_NHD, const void* a_saved, const void* b_saved,
+    const void* a_recomp, const void* b_recomp, void* gz_sorted, void* hs_sorted, float* gs_part,
+    momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
     if (g_sorted == nullptr || W2_NHD == nullptr || gz_sorted == nullptr || hs_sorted == nullptr || gs_part == nullptr)
@@ -523,8 +747,8 @@ extern "C" __attribute__((visibility("default"))) int momoe_dgrad2_swiglu_bwd(co
     if ((rc = encode_tmap_3d(&tmB, W2_NHD, plan->N, H, D, 128, TILE_K)) != MOMOE_OK) return rc;
     GemmArgs g;
     base_args(plan, g);
-    g.n_nblk = cdiv(H, 128);
-    g.nkb = cdiv(D, TILE_K);
+    g.n_nblk = cdiv(H, PAIR_N);
+    g.nkb = cdiv(D, KB);
     g.out_cols = H;
     g.out0 = static_cast<__nv_bfloat16*>(gz_sorted);
     g.out1 = static_cast<__nv_bfloat16*>(hs_sorted);
@@ -536,8 +760,9 @@ extern "C" __attribute__((visibility("default"))) int momoe_dgrad2_swiglu_bwd(co
     return launch<MODE_DGRAD2>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" __attribute__((visibility("default"))) int momoe_dgrad1(const momoe_plan_t* plan, const void* gz_sorted, const void* W1_ND2H, void* gx_sorted,
-                            momoe_stream_t stream) {
+extern "C" __attribute__((visibility("default"))) int momoe_dgrad1(const momoe_plan_t* plan, const void* gz_sorted,
+                                                                  const void* W1_ND2H, void* gx_sorted,
+                                                                  momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
     if (gz_sorted == nullptr || W1_ND2H == nullptr || gx_sorted == nullptr) return MOMOE_ERR_ARG;
@@ -545,18 +770,19 @@ extern "C" __attribute__((visibility("default"))) int momoe_dgrad1(const momoe_p
     CUtensorMap tmA, tmB;
     if ((rc = encode_tmap_2d(&tmA, gz_sorted, plan->rows_capacity, 2 * H, TILE_M, TILE_K)) != MOMOE_OK) return rc;
     // W1[e] is [D, 2H]: rows are the D output columns, 2H is the contiguous k axis
-    if ((rc = encode_tmap_3d(&tmB, W1_ND2H, plan->N, D, 2 * H, 256, TILE_K)) != MOMOE_OK) return rc;
+    if ((rc = encode_tmap_3d(&tmB, W1_ND2H, plan->N, D, 2 * H, 128, TILE_K)) != MOMOE_OK) return rc;
     GemmArgs g;
     base_args(plan, g);
-    g.n_nblk = cdiv(D, 256);
-    g.nkb = cdiv(2 * H, TILE_K);
+    g.n_nblk = cdiv(D, PAIR_N);
+    g.nkb = cdiv(2 * H, KB);
     g.out_cols = D;
     g.out0 = static_cast<__nv_bfloat16*>(gx_sorted);
     return launch<MODE_DGRAD1>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" __attribute__((visibility("default"))) int momoe_wgrad(const momoe_plan_t* plan, const void* a_sorted, int32_t X, const void* b_sorted, int32_t Y,
-                           void* dW_NXY, momoe_stream_t stream) {
+extern "C" __attribute__((visibility("default"))) int momoe_wgrad(const momoe_plan_t* plan, const void* a_sorted,
+                                                                 int32_t X, const void* b_sorted, int32_t Y,
+                                                                 void* dW_NXY, momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
     if (a_sorted == nullptr || b_sorted == nullptr || dW_NXY == nullptr || X <= 0 || Y <= 0) return MOMOE_ERR_ARG;
@@ -567,8 +793,8 @@ extern "C" __attribute__((visibility("default"))) int momoe_wgrad(const momoe_pl
     if ((rc = encode_tmap_2d(&tmB, b_sorted, plan->rows_capacity, Y, TILE_K, 64)) != MOMOE_OK) return rc;
     GemmArgs g;
     base_args(plan, g);
-    g.n_mblk = cdiv(X, TILE_M);
-    g.n_nblk = cdiv(Y, 256);
+    g.n_mblk = cdiv(X, 256);
+    g.n_nblk = cdiv(Y, PAIR_N);
     g.out_rows = X;
     g.out_cols = Y;
     g.out0 = static_cast<__nv_bfloat16*>(dW_NXY);

@@ -30,7 +30,7 @@ enum : int {
 };
 
 // sched[] layout (device int32[8]) written by the permutation builder and read by every later kernel.
-enum : int { SCHED_N_TILES = 0, SCHED_N_SAVED_TILES = 1, SCHED_PAD_ROWS = 2, SCHED_WORDS = 8 };
+enum : int { SCHED_N_TILES = 0, SCHED_N_SAVED_TILES = 1, SCHED_PAD_ROWS = 2, SCHED_N_PAIRS = 3, SCHED_WORDS = 8 };
 
 int sm_count();
 int encode_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,

@@ -181,9 +181,9 @@ __global__ void topk_from_mask_kernel(const int* __restrict__ mask, long long m_
 }
 
 // ------------------------------------------------------------------------------------------ permutation
-// Pass A: per-chunk histogram.  counts[c*N + e] = tokens of chunk c routed to expert e.
-__global__ void perm_count_kernel(const int* __restrict__ topk_idx, int M, int N, int K, int* __restrict__ counts,
-                                  int* status) {
+// Pass A: per-chunk histogram.  counts[e*n_chunks + c] = tokens of chunk c routed to expert e.
+__global__ void perm_count_kernel(const int* __restrict__ topk_idx, int M, int N, int K, int n_chunks,
+                                  int* __restrict__ counts, int* status) {
     extern __shared__ int sh[];
     const int warps = blockDim.x >> 5;
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -204,40 +204,59 @@ __global__ void perm_count_kernel(const int* __restrict__ topk_idx, int M, int N
         }
     }
     __syncwarp();
-    for (int e = lane; e < N; e += 32) counts[static_cast<size_t>(chunk) * N + e] = hist[e];
+    for (int e = lane; e < N; e += 32) counts[static_cast<size_t>(e) * n_chunks + chunk] = hist[e];
 }
 
 // Pass B (one block): per-expert exclusive scan over chunks (in place), then the expert-level tables.
 __global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, int N, int K, long long save_rows,
                                  long long* __restrict__ sizes, int* __restrict__ cumsums, int* __restrict__ pad_off,
-                                 int* __restrict__ tile_expert, int* __restrict__ sched, int tile_capacity) {
+                                 int* __restrict__ tile_expert, int* __restrict__ pair_info, int* __restrict__ sched,
+                                 int tile_capacity) {
     __shared__ int s_cnt[MAX_EXPERTS];
     __shared__ int s_cum[MAX_EXPERTS + 1];
     __shared__ int s_pad[MAX_EXPERTS + 1];
+    __shared__ int s_pair[MAX_EXPERTS + 1];   // first pair of each expert (a pair = two consecutive tiles of one expert)
     __shared__ int s_saved;
     const int e = threadIdx.x;
     if (e == 0) s_saved = 0;
-    int total = 0;
-    if (e < N) {
-        for (int c = 0; c < n_chunks; ++c) {
-            const int v = counts[static_cast<size_t>(c) * N + e];
-            counts[static_cast<size_t>(c) * N + e] = total;
-            total += v;
+    {   // one warp per expert (32 experts in flight): warp-wide exclusive scan over that expert's chunks
+        const int lane = threadIdx.x & 31;
+        for (int x = threadIdx.x >> 5; x < N; x += blockDim.x >> 5) {
+            int running = 0;
+            int* row = counts + static_cast<size_t>(x) * n_chunks;
+            for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+                const int c = c0 + lane;
+                const int v = c < n_chunks ? row[c] : 0;
+                int incl = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                if (c < n_chunks) row[c] = running + incl - v;
+                running += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) {
+                s_cnt[x] = running;
+                sizes[x] = running;
+            }
         }
-        s_cnt[e] = total;
-        sizes[e] = total;
     }
     __syncthreads();
     if (e == 0) {  // N <= 1024: a serial scan costs about a microsecond
-        int c = 0, p = 0;
+        int c = 0, p = 0, pr = 0;
         for (int i = 0; i < N; ++i) {
             s_cum[i] = c;
             s_pad[i] = p;
+            s_pair[i] = pr;
+            const int nt = (s_cnt[i] + TILE_M - 1) / TILE_M;
             c += s_cnt[i];
-            p += (s_cnt[i] + TILE_M - 1) / TILE_M * TILE_M;
+            p += nt * TILE_M;
+            pr += (nt + 1) / 2;
         }
         s_cum[N] = c;
         s_pad[N] = p;
+        s_pair[N] = pr;
     }
     __syncthreads();
     if (e < N) {
@@ -246,6 +265,9 @@ __global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, 
         const int ntile = (s_pad[e + 1] - s_pad[e]) / TILE_M;
         const int t0 = s_pad[e] / TILE_M;
         for (int t = 0; t < ntile && t0 + t < tile_capacity; ++t) tile_expert[t0 + t] = e;
+        // pair j of this expert covers tiles t0+2j and (when it exists) t0+2j+1: first tile * 2 + has-second
+        for (int j = 0; 2 * j < ntile && s_pair[e] + j < tile_capacity; ++j)
+            pair_info[s_pair[e] + j] = (t0 + 2 * j) * 2 + (2 * j + 1 < ntile ? 1 : 0);
         // tiles of this expert whose last row index (in the unpadded order) is below save_rows
         long long fit = (save_rows - s_cum[e]) / TILE_M;
         if (fit < 0) fit = 0;
@@ -259,7 +281,8 @@ __global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, 
         sched[SCHED_N_TILES] = s_pad[N] / TILE_M;
         sched[SCHED_N_SAVED_TILES] = s_saved;
         sched[SCHED_PAD_ROWS] = s_pad[N];
-        for (int i = 3; i < SCHED_WORDS; ++i) sched[i] = 0;
+        sched[SCHED_N_PAIRS] = s_pair[N];
+        for (int i = 4; i < SCHED_WORDS; ++i) sched[i] = 0;
     }
 }
 
@@ -267,7 +290,8 @@ __global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, 
 // chunk 32 tokens at a time and ranks the lanes that chose the same expert with a per-expert bit mask.
 __global__ void perm_fill_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
                                  const int* __restrict__ chunk_off, const int* __restrict__ cumsums,
-                                 const int* __restrict__ pad_off, int M, int N, int K, int* __restrict__ idx,
+                                 const int* __restrict__ pad_off, int M, int N, int K, int n_chunks,
+                                 int* __restrict__ idx,
                                  int* __restrict__ which, int* __restrict__ row_token, float* __restrict__ row_weight,
                                  int* __restrict__ pos) {
     extern __shared__ int sh[];
@@ -278,7 +302,7 @@ __global__ void perm_fill_kernel(const int* __restrict__ topk_idx, const float* 
     const int chunk = blockIdx.x * warps + w;
     const int m0 = chunk * CHUNK_TOKENS;
     if (m0 >= M) return;
-    for (int e = lane; e < N; e += 32) running[e] = chunk_off[static_cast<size_t>(chunk) * N + e];
+    for (int e = lane; e < N; e += 32) running[e] = chunk_off[static_cast<size_t>(e) * n_chunks + chunk];
     for (int g0 = 0; g0 < CHUNK_TOKENS; g0 += 32) {
         for (int e = lane; e < N; e += 32) bits[e] = 0u;
         __syncwarp();
@@ -480,11 +504,11 @@ extern "C" __attribute__((visibility("default"))) size_t momoe_permutation_works
 extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N,
                                        int32_t K, int64_t save_rows, int64_t* sizes_N, int32_t* cumsums_N1,
                                        int32_t* idx_Msum, int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert,
-                                       int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
+                                       int32_t* pair_info, int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
                                        int64_t rows_capacity, void* workspace, size_t workspace_bytes, int32_t* status,
                                        momoe_stream_t stream) {
     if (topk_idx_MK == nullptr || topk_w_MK == nullptr || sizes_N == nullptr || cumsums_N1 == nullptr ||
-        idx_Msum == nullptr || which_Msum == nullptr || pad_off == nullptr || tile_expert == nullptr ||
+        idx_Msum == nullptr || which_Msum == nullptr || pad_off == nullptr || tile_expert == nullptr || pair_info == nullptr ||
         sched == nullptr || row_token == nullptr || row_weight == nullptr || pos_MK == nullptr ||
         workspace == nullptr || status == nullptr)
         return MOMOE_ERR_ARG;
@@ -502,13 +526,14 @@ extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(co
     if (cudaMemsetAsync(row_token, 0xFF, sizeof(int32_t) * static_cast<size_t>(rows_capacity), st) != cudaSuccess ||
         cudaMemsetAsync(row_weight, 0, sizeof(float) * static_cast<size_t>(rows_capacity), st) != cudaSuccess)
         return MOMOE_ERR_CUDA;
-    perm_count_kernel<<<blocks, warps * 32, warps * N * sizeof(int), st>>>(topk_idx_MK, M, N, K, counts, status);
+    perm_count_kernel<<<blocks, warps * 32, warps * N * sizeof(int), st>>>(topk_idx_MK, M, N, K, static_cast<int>(n_chunks), counts, status);
     perm_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(counts, n_chunks, M, N, K, save_rows,
                                                 reinterpret_cast<long long*>(sizes_N), cumsums_N1, pad_off,
-                                                tile_expert, sched, static_cast<int>(momoe_tile_capacity(M, K, N)));
+                                                tile_expert, pair_info, sched,
+                                                static_cast<int>(momoe_tile_capacity(M, K, N)));
     perm_fill_kernel<<<blocks, warps * 32, warps * 2 * N * sizeof(int), st>>>(
-        topk_idx_MK, topk_w_MK, counts, cumsums_N1, pad_off, M, N, K, idx_Msum, which_Msum, row_token, row_weight,
-        pos_MK);
+        topk_idx_MK, topk_w_MK, counts, cumsums_N1, pad_off, M, N, K, static_cast<int>(n_chunks), idx_Msum, which_Msum,
+        row_token, row_weight, pos_MK);
     return LAUNCH_OK();
 }
 
@@ -616,10 +641,10 @@ static int perm_scratch_address(int** out) {
 extern "C" __attribute__((visibility("default"))) int momoe_build_permutation_static(
     const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N, int32_t K, int64_t save_rows,
     int64_t* sizes_N, int32_t* cumsums_N1, int32_t* idx_Msum, int32_t* which_Msum, int32_t* pad_off,
-    int32_t* tile_expert, int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
+    int32_t* tile_expert, int32_t* pair_info, int32_t* sched, int32_t* row_token, float* row_weight, int32_t* pos_MK,
     int64_t rows_capacity, int32_t* status, momoe_stream_t stream) {
     if (topk_idx_MK == nullptr || topk_w_MK == nullptr || sizes_N == nullptr || cumsums_N1 == nullptr ||
-        idx_Msum == nullptr || which_Msum == nullptr || pad_off == nullptr || tile_expert == nullptr ||
+        idx_Msum == nullptr || which_Msum == nullptr || pad_off == nullptr || tile_expert == nullptr || pair_info == nullptr ||
         sched == nullptr || row_token == nullptr || row_weight == nullptr || pos_MK == nullptr || status == nullptr)
         return MOMOE_ERR_ARG;
     if (M <= 0 || N <= 0 || K <= 0 || K > N || save_rows < 0) return MOMOE_ERR_ARG;
@@ -639,12 +664,13 @@ extern "C" __attribute__((visibility("default"))) int momoe_build_permutation_st
         return MOMOE_ERR_CUDA;
     // The array still holds the previous call's histogram.  Nothing has to be cleared: the first pass overwrites
     // every entry [chunk, expert] of the part this call uses before the later passes read it.
-    perm_count_kernel<<<blocks, warps * 32, warps * N * sizeof(int), st>>>(topk_idx_MK, M, N, K, counts, status);
+    perm_count_kernel<<<blocks, warps * 32, warps * N * sizeof(int), st>>>(topk_idx_MK, M, N, K, static_cast<int>(n_chunks), counts, status);
     perm_scan_kernel<<<1, MAX_EXPERTS, 0, st>>>(counts, static_cast<int>(n_chunks), M, N, K, save_rows,
                                                 reinterpret_cast<long long*>(sizes_N), cumsums_N1, pad_off,
-                                                tile_expert, sched, static_cast<int>(momoe_tile_capacity(M, K, N)));
+                                                tile_expert, pair_info, sched,
+                                                static_cast<int>(momoe_tile_capacity(M, K, N)));
     perm_fill_kernel<<<blocks, warps * 32, warps * 2 * N * sizeof(int), st>>>(
-        topk_idx_MK, topk_w_MK, counts, cumsums_N1, pad_off, M, N, K, idx_Msum, which_Msum, row_token, row_weight,
-        pos_MK);
+        topk_idx_MK, topk_w_MK, counts, cumsums_N1, pad_off, M, N, K, static_cast<int>(n_chunks), idx_Msum, which_Msum,
+        row_token, row_weight, pos_MK);
     return LAUNCH_OK();
 }

@@ -24,7 +24,7 @@ class Plan(C.Structure):
     """Mirror of momoe_plan_t."""
     _fields_ = [("M", c_i32), ("N", c_i32), ("K", c_i32), ("D", c_i32), ("H", c_i32), ("reserved", c_i32),
                 ("rows_capacity", c_i64), ("sched", c_vp), ("tile_expert", c_vp), ("pad_off", c_vp),
-                ("row_token", c_vp), ("row_weight", c_vp), ("pos_MK", c_vp), ("status", c_vp)]
+                ("row_token", c_vp), ("row_weight", c_vp), ("pos_MK", c_vp), ("status", c_vp), ("pair_info", c_vp)]
 
 
 PlanP = C.POINTER(Plan)
@@ -39,9 +39,9 @@ _PROTOS = {
                                        c_vp]),
     "momoe_permutation_workspace_bytes": (c_sz, [c_i32, c_i32, c_i32]),
     "momoe_build_permutation": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
-                                          c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_sz, c_vp, c_vp]),
+                                          c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_sz, c_vp, c_vp]),
     "momoe_build_permutation_static": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp,
-                                                 c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
+                                                 c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
     "momoe_gather_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_combine_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_up_swiglu": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),

@@ -77,6 +77,7 @@ class RoutingPlan:
         self.which = torch.empty(self.Msum, **i32)
         self.pad_off = torch.empty(N + 1, **i32)
         self.tile_expert = torch.empty(self.tile_capacity, **i32)
+        self.pair_info = torch.empty(self.tile_capacity, **i32)
         self.sched = torch.empty(8, **i32)
         self.row_token = torch.empty(self.rows_capacity, **i32)
         self.row_weight = torch.empty(self.rows_capacity, dtype=torch.float32, device=device)
@@ -88,7 +89,7 @@ class RoutingPlan:
                            sched=self.sched.data_ptr(), tile_expert=self.tile_expert.data_ptr(),
                            pad_off=self.pad_off.data_ptr(), row_token=self.row_token.data_ptr(),
                            row_weight=self.row_weight.data_ptr(), pos_MK=self.pos.data_ptr(),
-                           status=self.status.data_ptr())
+                           status=self.status.data_ptr(), pair_info=self.pair_info.data_ptr())
 
     @property
     def ref(self):
@@ -100,7 +101,7 @@ class RoutingPlan:
         ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=self.device)
         _call("momoe_build_permutation", 3, lib.momoe_build_permutation, ptr(topk_idx), ptr(topk_w), self.M, self.N, self.K, self.save_rows,
                                           ptr(self.sizes), ptr(self.cumsums), ptr(self.idx), ptr(self.which),
-                                          ptr(self.pad_off), ptr(self.tile_expert), ptr(self.sched),
+                                          ptr(self.pad_off), ptr(self.tile_expert), ptr(self.pair_info), ptr(self.sched),
                                           ptr(self.row_token), ptr(self.row_weight), ptr(self.pos),
                                           self.rows_capacity, ptr(ws), nbytes, ptr(self.status), stream_ptr())
         return self
@@ -198,7 +199,7 @@ def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=Tru
         a_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
         b_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
         _call("momoe_up_swiglu (recompute)", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2, stream_ptr())
-    n_part = (H + 127) // 128
+    n_part = 2 * ((H + 255) // 256)   # two partial sums per 256-column block (momoe_dgrad2_swiglu_bwd)
     gz = torch.empty((plan.rows_capacity, 2 * H), **bf)
     hs = torch.empty((plan.rows_capacity, H), **bf)
     gs_part = torch.empty((plan.rows_capacity, n_part), dtype=torch.float32, device=dev)

@@ -49,7 +49,7 @@ def test_bad_arguments_rejected_on_host(lib):
     assert L.momoe_route_topk(one, one, 4, 8, 2, 2, one, one, None, None, None, None, None, None) == -1
     assert L.momoe_topk_from_mask(None, 1, 1, None, 1, 1, 4, 8, 2, None, None, None, None) == -1
     plan = lib.Plan(M=4, N=8, K=2, D=60, H=32, reserved=0, rows_capacity=128 * 9, sched=16, tile_expert=16,
-                    pad_off=16, row_token=16, row_weight=16, pos_MK=16, status=16)
+                    pad_off=16, row_token=16, row_weight=16, pos_MK=16, status=16, pair_info=16)
     assert L.momoe_up_swiglu(C.byref(plan), one, one, one, None, None, 0, None) == -2   # D not a multiple of 8
     plan.D = 64
     assert L.momoe_up_swiglu(C.byref(plan), one, one, None, None, None, 0, None) == -1  # h missing

@@ -105,7 +105,7 @@ def test_backward_gemms(ops, M, N, K, D, H, skew, save_percent):
     a_r = torch.full((plan.recomp_tile_capacity * 128, H), float("nan"), **bf)
     b_r = torch.full((plan.recomp_tile_capacity * 128, H), float("nan"), **bf)
     _lib.check(L.momoe_up_swiglu(plan.ref, ptr(xs), ptr(W1), None, ptr(a_r), ptr(b_r), 2, st()), "up recompute")
-    n_part = (H + 127) // 128
+    n_part = 2 * ((H + 255) // 256)
     gz = torch.full((plan.rows_capacity, 2 * H), float("nan"), **bf)
     hs = torch.full((plan.rows_capacity, H), float("nan"), **bf)
     gsp = torch.full((plan.rows_capacity, n_part), float("nan"), dtype=torch.float32, device="cuda")

@@ -90,6 +90,13 @@ def test_permutation_bit_exact(ops, M, N, K, skew):
     assert sched[0] == exp_pad[-1] // 128 and sched[2] == exp_pad[-1]
     te = plan.tile_expert.cpu().numpy()[:sched[0]]
     assert np.array_equal(te, np.repeat(np.arange(N), (sizes + 127) // 128))
+    # pairs: two consecutive tiles of one expert, the last pair of an expert with an odd tile count is single
+    ntile = (sizes + 127) // 128
+    first = np.concatenate([[0], np.cumsum(ntile)])
+    exp_pairs = [int((first[e] + 2 * j) * 2 + (1 if 2 * j + 1 < ntile[e] else 0)) for e in range(N)
+                 for j in range((int(ntile[e]) + 1) // 2)]
+    assert sched[3] == len(exp_pairs)
+    assert plan.pair_info.cpu().numpy()[:sched[3]].tolist() == exp_pairs
     # tiles whose 128-row span (in the unpadded order) ends at or below save_rows
     ends = np.concatenate([cumsums[e] + 128 * (1 + np.arange((sizes[e] + 127) // 128)) for e in range(N)])
     assert sched[1] == int((ends <= plan.save_rows).sum())

@@ -34,6 +34,7 @@ class _Out:
         self.which = torch.full((M * K,), -7, **i32)
         self.pad_off = torch.full((N + 1,), -7, **i32)
         self.tile_expert = torch.full((tiles,), -7, **i32)
+        self.pair_info = torch.full((tiles,), -7, **i32)
         self.sched = torch.full((8,), -7, **i32)
         self.row_token = torch.full((self.rows,), -7, **i32)
         self.row_weight = torch.full((self.rows,), -7.0, dtype=torch.float32, device="cuda")
@@ -41,7 +42,8 @@ class _Out:
 
     def tensors(self, n_tiles=None):
         te = self.tile_expert if n_tiles is None else self.tile_expert[:n_tiles]
-        return [self.sizes, self.cumsums, self.idx, self.which, self.pad_off, te, self.sched, self.row_token,
+        pi = self.pair_info if n_tiles is None else self.pair_info[:int(self.sched[3])]
+        return [self.sizes, self.cumsums, self.idx, self.which, self.pad_off, te, pi, self.sched, self.row_token,
                 self.row_weight, self.pos]
 
 
@@ -54,11 +56,11 @@ def _run_both(_lib, M, N, K, seed, save_rows):
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     st = _lib.stream_ptr()
     rc = L.momoe_build_permutation(p(topk_idx), p(topk_w), M, N, K, save_rows, p(a.sizes), p(a.cumsums), p(a.idx),
-                                   p(a.which), p(a.pad_off), p(a.tile_expert), p(a.sched), p(a.row_token),
+                                   p(a.which), p(a.pad_off), p(a.tile_expert), p(a.pair_info), p(a.sched), p(a.row_token),
                                    p(a.row_weight), p(a.pos), a.rows, p(ws), nbytes, p(status), st)
     assert rc == 0
     rc = L.momoe_build_permutation_static(p(topk_idx), p(topk_w), M, N, K, save_rows, p(b.sizes), p(b.cumsums),
-                                          p(b.idx), p(b.which), p(b.pad_off), p(b.tile_expert), p(b.sched),
+                                          p(b.idx), p(b.which), p(b.pad_off), p(b.tile_expert), p(b.pair_info), p(b.sched),
                                           p(b.row_token), p(b.row_weight), p(b.pos), b.rows, p(status), st)
     assert rc == 0
     torch.cuda.synchronize()
@@ -83,6 +85,6 @@ def test_static_scratch_rejects_problems_beyond_its_capacity(libs):
     one = C.c_void_p(16)   # never dereferenced: validation fails first
     M, N, K = 65536 + 64, 256, 8
     rows = int(L.momoe_sorted_rows_capacity(M, K, N))
-    args = [one, one, M, N, K, 0] + [one] * 10 + [rows, one, None]
+    args = [one, one, M, N, K, 0] + [one] * 11 + [rows, one, None]
     assert L.momoe_build_permutation_static(*args) == -4
     assert L.momoe_build_permutation_static(None, *args[1:]) == -1
