@@ -159,6 +159,54 @@ int momoe_router_backward(const float* G_s, int64_t gs_stride_n, int64_t gs_stri
                           const float* s_MN, const float* Ng_M, const float* Ks_M, const int32_t* mask_NM,
                           int32_t M, int32_t N, int32_t Ks, void* G_logits_MN, momoe_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * Expert parallelism over peer memory (no counterpart in the reference, whose README lists expert parallelism as
+ * unsupported).  R <= 8 ranks of one NVLink node, one process per GPU; rank r owns experts [r*N/R, (r+1)*N/R).
+ * `peer_*` arguments are HOST arrays of R device pointers: entry p is rank p's buffer, mapped into this process
+ * (entry [rank] is the local one).  The flag arrays (uint32[8] per rank) must start zeroed; `epoch` must grow by one
+ * with every hand-shake, identically on every rank.  Waits on a peer are bounded (status 301 when they run out).
+ * ------------------------------------------------------------------------------------------------------------ */
+
+/* Store this rank's per-expert token counts (sizes_N of momoe_build_permutation) into row `rank` of every peer's
+ * int32[R*N] counts matrix, then hand-shake: on return (in stream order) this rank's matrix is complete. */
+int momoe_ep_publish_counts(const int64_t* sizes_N, int32_t N, void* const* peer_counts, void* const* peer_flags,
+                            int32_t world, int32_t rank, uint32_t epoch, int32_t* status, momoe_stream_t stream);
+
+/* Hand-shake only: every rank has executed everything it queued before this call. */
+int momoe_ep_barrier(void* const* peer_flags, int32_t world, int32_t rank, uint32_t epoch, int32_t* status,
+                     momoe_stream_t stream);
+
+/* From the complete counts matrix, on the device: the padded expert-major layout of this rank's expert block
+ * (local_count int32[N/R], pad_off int32[N/R+1], tile_expert, pair_info, sched: the tables of momoe_plan_t, with
+ * sched[1] following save_percent of the rows this rank received), dst_base_N int32[N] (row inside the owner's layout
+ * where this rank's tokens for each expert start; -1 everywhere and status 302 if some rank would exceed cap_rows),
+ * and sizes_global_N int64[N] (tokens per expert summed over ranks: the layer's tokens_per_expert_N). */
+int momoe_ep_plan(const int32_t* counts_RN, int32_t world, int32_t rank, int32_t N, double save_percent,
+                  int64_t cap_rows, int32_t* dst_base_N, int64_t* sizes_global_N, int32_t* local_count,
+                  int32_t* pad_off, int32_t* tile_expert, int32_t* pair_info, int32_t* sched, int32_t* status,
+                  momoe_stream_t stream);
+
+/* Gather + send: row src[token,:] of every (token, expert) pair of `home` (this rank's own permutation over all N
+ * experts) is stored into the owner's expert-major buffer at dst_base_N[e] + (index among this rank's tokens of e);
+ * peer_row_weight (may be NULL) receives the routing weight, remote_row (may be NULL, int32[home rows_capacity])
+ * the row used.  Also zeroes the padding rows of this rank's own buffer. */
+int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int32_t cols, const int32_t* dst_base_N,
+                           int32_t experts_per_rank, void* const* peer_rows, void* const* peer_row_weight,
+                           int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
+                           const int32_t* local_pad_off, momoe_stream_t stream);
+
+/* Receive + reduce: dst[m,:] = bf16(sum_k rows@owner(m,k)[remote_row,:]), fp32 accumulation in ascending k. */
+int momoe_ep_combine_rows(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
+                          int32_t experts_per_rank, int32_t cols, void* dst, int32_t world, momoe_stream_t stream);
+
+/* row_gs[r] = sum of the dgrad-2 partial sums of local row r. */
+int momoe_ep_reduce_gs(const float* gs_part, int32_t n_part, const int32_t* sched, float* row_gs,
+                       momoe_stream_t stream);
+
+/* Dense G_s_NM fp32 [N,M] of this rank's tokens (zero where unselected), pulled from the owners' row_gs. */
+int momoe_ep_pull_gs(const momoe_plan_t* home, void* const* peer_row_gs, const int32_t* remote_row,
+                     int32_t experts_per_rank, float* G_s_NM, int32_t world, momoe_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

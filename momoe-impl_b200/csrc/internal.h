@@ -27,6 +27,8 @@ enum : int {
     DEV_TIMEOUT_EPILOGUE = 103,
     DEV_BAD_TOPK_COUNT = 201,   // a token does not have exactly K experts in mask_NM
     DEV_BAD_EXPERT_ID = 202,
+    DEV_TIMEOUT_PEER = 301,     // a peer rank did not reach the hand-shake in time
+    DEV_EP_OVERFLOW = 302,      // a rank would receive more rows than its buffers hold
 };
 
 // sched[] layout (device int32[8]) written by the permutation builder and read by every later kernel.

@@ -17,7 +17,7 @@ if not os.path.exists(LIB_PATH):
 
 lib = C.CDLL(LIB_PATH)
 
-c_i32, c_i64, c_vp, c_sz = C.c_int32, C.c_int64, C.c_void_p, C.c_size_t
+c_i32, c_i64, c_vp, c_sz, c_u32 = C.c_int32, C.c_int64, C.c_void_p, C.c_size_t, C.c_uint32
 
 
 class Plan(C.Structure):
@@ -52,6 +52,15 @@ _PROTOS = {
     "momoe_scatter_gs": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_router_backward": (C.c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp,
                                         c_vp]),
+    "momoe_ep_publish_counts": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_u32, c_vp, c_vp]),
+    "momoe_ep_barrier": (C.c_int, [c_vp, c_i32, c_i32, c_u32, c_vp, c_vp]),
+    "momoe_ep_plan": (C.c_int, [c_vp, c_i32, c_i32, c_i32, C.c_double, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+                                c_vp, c_vp]),
+    "momoe_ep_dispatch_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp,
+                                         c_vp]),
+    "momoe_ep_combine_rows": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_i32, c_vp, c_i32, c_vp]),
+    "momoe_ep_reduce_gs": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_vp]),
+    "momoe_ep_pull_gs": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp]),
 }
 for _name, (_res, _args) in _PROTOS.items():
     _f = getattr(lib, _name)

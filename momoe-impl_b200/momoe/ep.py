@@ -1,17 +1,19 @@
 """Expert parallelism for the MoMoE layer (the reference has none; its README lists it as unsupported).
 
 Rank r of an R-rank group owns the contiguous expert block [r*N/R, (r+1)*N/R) and keeps its own tokens
-(data parallel).  One forward pass does
+(data parallel).  Two transports:
 
-    route locally -> gather rows into expert-major order (already grouped by destination rank)
-    -> all-gather of the per-expert counts (the only host synchronisation: NCCL needs split sizes)
-    -> all-to-all of rows and routing weights -> local grouped GEMMs on the received rows
-    -> all-to-all back -> combine at the token's home rank.
+* ``"peer"`` (default inside one NVLink node): buffers every rank can address (torch symmetric memory).  The
+  per-expert counts are exchanged by peer stores and a flag hand-shake, every rank derives the whole dispatch plan on
+  the device, token rows are stored straight into the owner's padded expert-major buffer (gather + send in one
+  kernel) and results are summed straight out of the owners' buffers (receive + reduce in one kernel).  The host
+  never synchronises and nothing is staged.
+* ``"nccl"``: all-gather of counts (one host synchronisation for the split sizes), all-to-all-v of rows, local
+  re-sort.  Works wherever NCCL does; `DispatchMeta` holds its index arithmetic (device-agnostic torch ops, tested
+  with CPU ranks).
 
-Backward mirrors it with the upstream gradient.  Payload always lands in the receiving GPU's own memory and is
-read from there by the local kernels; no kernel touches a peer's memory.
-
-`DispatchMeta` holds the pure index arithmetic (device-agnostic torch ops), so it is testable with CPU ranks.
+Backward mirrors forward with the upstream gradient.  Payload always lands in the owner's own memory before the
+grouped GEMMs read it; no TMA load ever addresses a peer.
 """
 import ctypes as C
 
@@ -176,13 +178,180 @@ class ExpertParallelFunction(torch.autograd.Function):
         return (G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_s.to(s_dev), None, None, None, None, None)
 
 
+class PeerBuffers:
+    """Symmetric (peer-addressable) buffers of one expert-parallel layer and the epoch counter of its hand-shakes."""
+
+    def __init__(self, group, device, N, D, cap_rows):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.cap_rows = cap_rows
+        self.epoch = 0
+        self._keep = []
+
+        def alloc(shape, dtype):
+            t = symm_mem.empty(shape, dtype=dtype, device=device)
+            t.zero_()
+            h = symm_mem.rendezvous(t, group)
+            self._keep.append(h)
+            arr = (C.c_void_p * self.world)(*[C.c_void_p(int(p)) for p in h.buffer_ptrs])
+            return t, arr
+
+        self.rows_x, self.p_rows_x = alloc((cap_rows, D), torch.bfloat16)     # dispatched activations (kept for backward)
+        self.rows_y, self.p_rows_y = alloc((cap_rows, D), torch.bfloat16)     # expert outputs / input gradients
+        self.rows_g, self.p_rows_g = alloc((cap_rows, D), torch.bfloat16)     # dispatched upstream gradient
+        self.row_w, self.p_row_w = alloc((cap_rows,), torch.float32)          # routing weight of each received row
+        self.row_gs, self.p_row_gs = alloc((cap_rows,), torch.float32)        # dL/ds of each received row
+        self.counts, self.p_counts = alloc((self.world * N,), torch.int32)
+        self.flags, self.p_flags = alloc((8,), torch.int32)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)     # every rank's buffers are zeroed before anybody signals
+
+    def next_epoch(self):
+        self.epoch += 1
+        return self.epoch
+
+
+class PeerExpertParallelFunction(torch.autograd.Function):
+    """Expert computation with dispatch / combine over peer memory (see the module docstring)."""
+
+    @staticmethod
+    def forward(ctx, x_BSD, W1_local, W2_local, mask_NM, s_NM, topk_idx, topk_w, K, save_percent, bufs):
+        from . import _lib, ops
+        lib, ptr, st = _lib.lib, _lib.ptr, _lib.stream_ptr
+        B, S, D = x_BSD.shape
+        M = B * S
+        dev = W1_local.device
+        Nl, H, _ = W2_local.shape
+        R, rank = bufs.world, bufs.rank
+        N = Nl * R
+        cap = bufs.cap_rows
+        i32 = dict(dtype=torch.int32, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        x_MD = x_BSD.reshape(M, D).to(device=dev, dtype=torch.bfloat16).contiguous()
+        W1 = W1_local.detach().to(torch.bfloat16).contiguous()
+        W2 = W2_local.detach().to(torch.bfloat16).contiguous()
+        with torch.cuda.device(dev):
+            home = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, H, 0.0)
+            status = home.status
+            ops._call("momoe_ep_publish_counts", 1, lib.momoe_ep_publish_counts, ptr(home.sizes), N, bufs.p_counts,
+                      bufs.p_flags, R, rank, bufs.next_epoch(), ptr(status), st())
+            tile_cap = cap // ops.TILE_M
+            dst_base = torch.empty(N, **i32)
+            sizes_global = torch.empty(N, dtype=torch.int64, device=dev)
+            local_count = torch.empty(Nl, **i32)
+            pad_off = torch.empty(Nl + 1, **i32)
+            tile_expert = torch.empty(tile_cap, **i32)
+            pair_info = torch.empty(tile_cap, **i32)
+            sched = torch.empty(8, **i32)
+            ops._call("momoe_ep_plan", 1, lib.momoe_ep_plan, ptr(bufs.counts), R, rank, N, float(save_percent), cap,
+                      ptr(dst_base), ptr(sizes_global), ptr(local_count), ptr(pad_off), ptr(tile_expert),
+                      ptr(pair_info), ptr(sched), ptr(status), st())
+            local = _lib.Plan(M=1, N=Nl, K=1, D=D, H=H, reserved=0, rows_capacity=cap, sched=sched.data_ptr(),
+                              tile_expert=tile_expert.data_ptr(), pad_off=pad_off.data_ptr(), row_token=0,
+                              row_weight=bufs.row_w.data_ptr(), pos_MK=0, status=status.data_ptr(),
+                              pair_info=pair_info.data_ptr())
+            remote_row = torch.empty(home.rows_capacity, **i32)
+            ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows, home.ref, ptr(x_MD), D, ptr(dst_base),
+                      Nl, bufs.p_rows_x, bufs.p_row_w, ptr(remote_row), R, rank, ptr(local_count), ptr(pad_off),
+                      st())
+            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                      ptr(status), st())
+            # local experts on the received rows: already expert-major and padded
+            h = torch.empty((cap, H), **bf)
+            a_save = b_save = None
+            mode = 0
+            if save_percent > 0:
+                a_save = torch.empty((cap, H), **bf)
+                b_save = torch.empty((cap, H), **bf)
+                mode = 1
+            ops._call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, C.byref(local), ptr(bufs.rows_x), ptr(W1), ptr(h),
+                      ptr(a_save), ptr(b_save), mode, st())
+            ops._call("momoe_down_scale", 1, lib.momoe_down_scale, C.byref(local), ptr(h), ptr(W2), ptr(bufs.rows_y),
+                      st())
+            del h
+            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                      ptr(status), st())
+            y_MD = torch.empty((M, D), **bf)
+            ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y, ptr(remote_row),
+                      Nl, D, ptr(y_MD), R, st())
+        ctx.bufs, ctx.home, ctx.local = bufs, home, local
+        ctx.keep = (dst_base, local_count, pad_off, tile_expert, pair_info, sched, remote_row)
+        ctx.shape = (B, S, D)
+        ctx.dims = (N, Nl, H, K)
+        ctx.save_percent = save_percent
+        ctx.in_devices = (x_BSD.device, s_NM.device)
+        ctx.has_ab = a_save is not None
+        ctx.save_for_backward(*([W1, W2] + ([a_save, b_save] if ctx.has_ab else [])))
+        ctx.mark_non_differentiable(sizes_global)
+        return y_MD.reshape(B, S, D).to(x_BSD.device), sizes_global
+
+    @staticmethod
+    def backward(ctx, G_y_BSD, _):
+        from . import _lib, ops
+        lib, ptr, st = _lib.lib, _lib.ptr, _lib.stream_ptr
+        saved = ctx.saved_tensors
+        W1, W2 = saved[:2]
+        a_save, b_save = (saved[2], saved[3]) if ctx.has_ab else (None, None)
+        B, S, D = ctx.shape
+        N, Nl, H, K = ctx.dims
+        M = B * S
+        bufs, home, local = ctx.bufs, ctx.home, ctx.local
+        dst_base, local_count, pad_off, tile_expert, pair_info, sched, remote_row = ctx.keep
+        R, rank, cap = bufs.world, bufs.rank, bufs.cap_rows
+        dev = W1.device
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        status = home.status
+        g_MD = G_y_BSD.reshape(M, D).to(device=dev, dtype=torch.bfloat16).contiguous()
+        with torch.cuda.device(dev):
+            ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows, home.ref, ptr(g_MD), D, ptr(dst_base),
+                      Nl, bufs.p_rows_g, None, None, R, rank, ptr(local_count), ptr(pad_off), st())
+            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                      ptr(status), st())
+            lp = C.byref(local)
+            # Tiles that do not lie entirely below the save boundary are recomputed; even at save_percent = 100 the
+            # last partial tile of an expert can be one of them, so the pass always runs (it skips saved tiles).
+            rec_tiles = min(cap // ops.TILE_M,
+                            int(cap * (100.0 - ctx.save_percent) / 100.0) // ops.TILE_M + Nl + 1)
+            a_rec = torch.empty((rec_tiles * ops.TILE_M, H), **bf)
+            b_rec = torch.empty((rec_tiles * ops.TILE_M, H), **bf)
+            ops._call("momoe_up_swiglu (recompute)", 1, lib.momoe_up_swiglu, lp, ptr(bufs.rows_x), ptr(W1), None,
+                      ptr(a_rec), ptr(b_rec), 2, st())
+            n_part = 2 * ((H + 255) // 256)
+            gz = torch.empty((cap, 2 * H), **bf)
+            hs = torch.empty((cap, H), **bf)
+            gs_part = torch.empty((cap, n_part), dtype=torch.float32, device=dev)
+            ops._call("momoe_dgrad2_swiglu_bwd", 1, lib.momoe_dgrad2_swiglu_bwd, lp, ptr(bufs.rows_g), ptr(W2),
+                      ptr(a_save), ptr(b_save), ptr(a_rec), ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), st())
+            del a_rec, b_rec
+            G_W2 = torch.empty_like(W2)
+            ops._call("momoe_wgrad (W2)", 1, lib.momoe_wgrad, lp, ptr(hs), H, ptr(bufs.rows_g), D, ptr(G_W2), st())
+            G_W1 = torch.empty_like(W1)
+            ops._call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, lp, ptr(bufs.rows_x), D, ptr(gz), 2 * H, ptr(G_W1), st())
+            ops._call("momoe_dgrad1", 1, lib.momoe_dgrad1, lp, ptr(gz), ptr(W1), ptr(bufs.rows_y), st())
+            ops._call("momoe_ep_reduce_gs", 1, lib.momoe_ep_reduce_gs, ptr(gs_part), n_part, ptr(sched),
+                      ptr(bufs.row_gs), st())
+            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                      ptr(status), st())
+            G_x = torch.empty((M, D), **bf)
+            ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y, ptr(remote_row),
+                      Nl, D, ptr(G_x), R, st())
+            G_s = torch.empty((N, M), dtype=torch.float32, device=dev)
+            ops._call("momoe_ep_pull_gs", 1, lib.momoe_ep_pull_gs, home.ref, bufs.p_row_gs, ptr(remote_row), Nl,
+                      ptr(G_s), R, st())
+        x_dev, s_dev = ctx.in_devices
+        return (G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_s.to(s_dev), None, None, None, None, None)
+
+
 class ExpertParallelMoE(nn.Module):
     """`MoE` with the experts sharded over a process group: same forward signature and bias update; the router is
     replicated, `Wl1_ND2H` / `Wl2_NHD` hold this rank's block of N/R experts, and `tokens_per_expert_N` (which drives
     the bias update) is the global count summed over ranks."""
 
     def __init__(self, embedding_dim, intermediate_dim, num_experts, num_chosen_experts, num_shared_experts,
-                 save_percent=0, bias_update_rate=1e-4, Wg_DN=None, Wl1_ND2H=None, Wl2_NHD=None, *, group=None):
+                 save_percent=0, bias_update_rate=1e-4, Wg_DN=None, Wl1_ND2H=None, Wl2_NHD=None, *, group=None,
+                 transport="peer", capacity_factor=2.0):
         super().__init__()
         assert save_percent >= 0 and save_percent <= 100, \
             "save_percent must be between 0 and 100 inclusive, got {}".format(save_percent)
@@ -193,6 +362,10 @@ class ExpertParallelMoE(nn.Module):
                                                    num_shared_experts)
         self.save_percent = save_percent
         self.bias_update_rate = bias_update_rate
+        assert transport in ("peer", "nccl")
+        self.transport = transport
+        self.capacity_factor = capacity_factor
+        self._bufs = None
         Nl = num_experts // R
         self.router = TopKRouter(embedding_dim, num_experts, num_chosen_experts, num_shared_experts, Wg_DN=Wg_DN)
         dev = self.router.Wg_DN.device
@@ -211,10 +384,26 @@ class ExpertParallelMoE(nn.Module):
     def forward(self, x_BSD):
         x_BSD, mask_NM, s_NM = self.router(x_BSD, self.biases_N)
         topk_idx, topk_w = mask_NM._momoe_topk
-        y_BSD, sizes_N = ExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM, topk_idx,
-                                                      topk_w, self.K, self.save_percent, self.group)
         B, S, _ = x_BSD.shape
+        if self.transport == "peer":
+            bufs = self._peer_buffers(B * S)
+            y_BSD, sizes_N = PeerExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM,
+                                                              topk_idx, topk_w, self.K, self.save_percent, bufs)
+        else:
+            y_BSD, sizes_N = ExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM, topk_idx,
+                                                          topk_w, self.K, self.save_percent, self.group)
         R = dist.get_world_size(self.group)
         c_avg = B * S * R * (self.K - self.Ks) / (self.N - self.Ks)
         self.biases_N += self.bias_update_rate * torch.sign(c_avg - sizes_N.to(self.biases_N.device))
         return y_BSD
+
+    def _peer_buffers(self, M):
+        """Symmetric buffers sized for `capacity_factor` times the average number of rows a rank receives (plus one
+        partial tile per local expert); allocated collectively on first use and whenever more tokens arrive."""
+        R = dist.get_world_size(self.group)
+        Nl = self.N // R
+        want = int(M * self.K * self.capacity_factor) + Nl * 128
+        want = (want + 127) // 128 * 128
+        if self._bufs is None or self._bufs.cap_rows < want:
+            self._bufs = PeerBuffers(self.group, self.Wl1_ND2H.device, self.N, self.D, want)
+        return self._bufs

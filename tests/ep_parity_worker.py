@@ -15,6 +15,52 @@ sys.path.insert(0, os.path.join(ROOT, "momoe-impl_b200"))
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
+def run_case(transport, case, rank, world, dev, momoe, ep, ops, cos, max_rel):
+    Mr, D, H, N, K, Ks, sp, bias_std = case
+    g = torch.Generator().manual_seed(1234 + D)
+    x_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
+    W1 = (torch.randn(N, D, 2 * H, generator=g) * 0.03).bfloat16()
+    W2 = (torch.randn(N, H, D, generator=g) * 0.03).bfloat16()
+    Wg = (torch.randn(D, N, generator=g) * 0.05).bfloat16()
+    gy_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
+    biases = torch.cat([torch.randn(N - Ks, generator=g) * bias_std, torch.full((Ks,), float("-inf"))])
+    Nl = N // world
+    # (a) single GPU, all tokens
+    ref = momoe.MoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
+                    Wl1_ND2H=W1.to(dev), Wl2_NHD=W2.to(dev))
+    with torch.no_grad():
+        ref.biases_N.copy_(biases.to(dev))
+    xa = x_all.reshape(1, world * Mr, D).to(dev).requires_grad_(True)
+    ya = ref(xa)
+    ya.backward(gy_all.reshape(1, world * Mr, D).to(dev))
+    # (b) expert parallel, own shard
+    moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
+                               Wl1_ND2H=W1[rank * Nl:(rank + 1) * Nl].to(dev),
+                               Wl2_NHD=W2[rank * Nl:(rank + 1) * Nl].to(dev), transport=transport)
+    with torch.no_grad():
+        moe.biases_N.copy_(biases.to(dev))
+    xr = x_all[rank].to(dev).requires_grad_(True)
+    yr = moe(xr)
+    yr.backward(gy_all[rank].to(dev))
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    sl = slice(rank * Mr, (rank + 1) * Mr)
+    assert torch.equal(moe.biases_N, ref.biases_N), "bias update (global tokens_per_expert) differs"
+    # same kernels, same per-row arithmetic: y rows are identical bits
+    assert torch.equal(yr[0], ya[0, sl]), "y differs: max-rel %g" % max_rel(yr[0], ya[0, sl])
+    assert cos(xr.grad[0], xa.grad[0, sl]) > 0.9999 and max_rel(xr.grad[0], xa.grad[0, sl]) < 2e-2
+    for name, got, full in (("W1", moe.Wl1_ND2H.grad, ref.momoe.Wl1_ND2H.grad),
+                            ("W2", moe.Wl2_NHD.grad, ref.momoe.Wl2_NHD.grad)):
+        want = full[rank * Nl:(rank + 1) * Nl]
+        assert cos(got, want) > 0.9999, name
+        assert max_rel(got, want) < 2e-2, name
+    gwg = moe.router.Wg_DN.grad.float().clone()
+    dist.all_reduce(gwg)
+    assert cos(gwg, ref.router.Wg_DN.grad) > 0.999
+    if rank == 0:
+        print("ep parity ok:", transport, (Mr, D, H, N, K, Ks, sp), "world", world, flush=True)
+
+
 def main():
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -31,49 +77,9 @@ def main():
         (1000, 512, 256, 16, 4, 0, 50, 0.05),
         (512, 384, 136, 8, 3, 1, 100, 0.02),
     ]
-    for (Mr, D, H, N, K, Ks, sp, bias_std) in cases:
-        g = torch.Generator().manual_seed(1234 + D)
-        x_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
-        W1 = (torch.randn(N, D, 2 * H, generator=g) * 0.03).bfloat16()
-        W2 = (torch.randn(N, H, D, generator=g) * 0.03).bfloat16()
-        Wg = (torch.randn(D, N, generator=g) * 0.05).bfloat16()
-        gy_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
-        biases = torch.cat([torch.randn(N - Ks, generator=g) * bias_std, torch.full((Ks,), float("-inf"))])
-        Nl = N // world
-        # (a) single GPU, all tokens
-        ref = momoe.MoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
-                        Wl1_ND2H=W1.to(dev), Wl2_NHD=W2.to(dev))
-        with torch.no_grad():
-            ref.biases_N.copy_(biases.to(dev))
-        xa = x_all.reshape(1, world * Mr, D).to(dev).requires_grad_(True)
-        ya = ref(xa)
-        ya.backward(gy_all.reshape(1, world * Mr, D).to(dev))
-        # (b) expert parallel, own shard
-        moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
-                                   Wl1_ND2H=W1[rank * Nl:(rank + 1) * Nl].to(dev),
-                                   Wl2_NHD=W2[rank * Nl:(rank + 1) * Nl].to(dev))
-        with torch.no_grad():
-            moe.biases_N.copy_(biases.to(dev))
-        xr = x_all[rank].to(dev).requires_grad_(True)
-        yr = moe(xr)
-        yr.backward(gy_all[rank].to(dev))
-        torch.cuda.synchronize()
-        ops.check_status(dev)
-        sl = slice(rank * Mr, (rank + 1) * Mr)
-        assert torch.equal(moe.biases_N, ref.biases_N), "bias update (global tokens_per_expert) differs"
-        # same kernels, same per-row arithmetic: y rows are identical bits
-        assert torch.equal(yr[0], ya[0, sl]), "y differs: max-rel %g" % max_rel(yr[0], ya[0, sl])
-        assert cos(xr.grad[0], xa.grad[0, sl]) > 0.9999 and max_rel(xr.grad[0], xa.grad[0, sl]) < 2e-2
-        for name, got, full in (("W1", moe.Wl1_ND2H.grad, ref.momoe.Wl1_ND2H.grad),
-                                ("W2", moe.Wl2_NHD.grad, ref.momoe.Wl2_NHD.grad)):
-            want = full[rank * Nl:(rank + 1) * Nl]
-            assert cos(got, want) > 0.9999, name
-            assert max_rel(got, want) < 2e-2, name
-        gwg = moe.router.Wg_DN.grad.float().clone()
-        dist.all_reduce(gwg)
-        assert cos(gwg, ref.router.Wg_DN.grad) > 0.999
-        if rank == 0:
-            print("ep parity ok:", (Mr, D, H, N, K, Ks, sp), "world", world, flush=True)
+    for transport in ("peer", "nccl"):
+        for case in cases:
+            run_case(transport, case, rank, world, dev, momoe, ep, ops, cos, max_rel)
     dist.barrier()
     dist.destroy_process_group()
 
