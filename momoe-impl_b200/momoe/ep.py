@@ -402,7 +402,8 @@ class ExpertParallelMoE(nn.Module):
         partial tile per local expert); allocated collectively on first use and whenever more tokens arrive."""
         R = dist.get_world_size(self.group)
         Nl = self.N // R
-        want = int(M * self.K * self.capacity_factor) + Nl * 128
+        # routed experts: capacity_factor x the balanced share; shared experts receive every token of every rank
+        want = int(M * (self.K - self.Ks) * self.capacity_factor) + R * M * self.Ks + Nl * 128
         want = (want + 127) // 128 * 128
         if self._bufs is None or self._bufs.cap_rows < want:
             self._bufs = PeerBuffers(self.group, self.Wl1_ND2H.device, self.N, self.D, want)
