@@ -189,15 +189,19 @@ int momoe_ep_plan(const int32_t* counts_RN, int32_t world, int32_t rank, int32_t
 /* Gather + send: row src[token,:] of every (token, expert) pair of `home` (this rank's own permutation over all N
  * experts) is stored into the owner's expert-major buffer at dst_base_N[e] + (index among this rank's tokens of e);
  * peer_row_weight (may be NULL) receives the routing weight, remote_row (may be NULL, int32[home rows_capacity])
- * the row used.  Also zeroes the padding rows of this rank's own buffer. */
+ * the row used.  Also zeroes the padding rows of this rank's own buffer.
+ * max_blocks (here and in momoe_ep_combine_rows): 0 = size the grid for the whole GPU; one block of 256 threads per
+ * SM (max_blocks = SM count) is enough to fill NVLink and leaves room for a grouped GEMM, queued on another stream,
+ * to run on the same SMs at the same time. */
 int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int32_t cols, const int32_t* dst_base_N,
                            int32_t experts_per_rank, void* const* peer_rows, void* const* peer_row_weight,
                            int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
-                           const int32_t* local_pad_off, momoe_stream_t stream);
+                           const int32_t* local_pad_off, int32_t max_blocks, momoe_stream_t stream);
 
 /* Receive + reduce: dst[m,:] = bf16(sum_k rows@owner(m,k)[remote_row,:]), fp32 accumulation in ascending k. */
 int momoe_ep_combine_rows(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
-                          int32_t experts_per_rank, int32_t cols, void* dst, int32_t world, momoe_stream_t stream);
+                          int32_t experts_per_rank, int32_t cols, void* dst, int32_t world, int32_t max_blocks,
+                          momoe_stream_t stream);
 
 /* row_gs[r] = sum of the dgrad-2 partial sums of local row r. */
 int momoe_ep_reduce_gs(const float* gs_part, int32_t n_part, const int32_t* sched, float* row_gs,

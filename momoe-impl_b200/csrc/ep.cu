@@ -355,7 +355,7 @@ EP_API int momoe_ep_plan(const int32_t* counts_RN, int32_t world, int32_t rank, 
 EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int32_t cols, const int32_t* dst_base_N,
                                   int32_t experts_per_rank, void* const* peer_rows, void* const* peer_row_weight,
                                   int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
-                                  const int32_t* local_pad_off, momoe_stream_t stream) {
+                                  const int32_t* local_pad_off, int32_t max_blocks, momoe_stream_t stream) {
     if (home == nullptr || src == nullptr || dst_base_N == nullptr || peer_rows == nullptr || local_count == nullptr ||
         local_pad_off == nullptr || home->row_token == nullptr || home->tile_expert == nullptr ||
         home->pad_off == nullptr || home->sched == nullptr || home->row_weight == nullptr)
@@ -365,14 +365,15 @@ EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int
     PeerPtrs r, w;
     if (fill_peers(r, peer_rows, world) != MOMOE_OK || fill_peers(w, peer_row_weight, world) != MOMOE_OK)
         return MOMOE_ERR_ARG;
-    ep_dispatch_rows_kernel<<<sm_count() * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    const int grid = max_blocks > 0 ? max_blocks : sm_count() * 8;
+    ep_dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(src), home->row_token, home->tile_expert, home->pad_off, home->sched,
         home->row_weight, dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, local_count, local_pad_off);
     return EP_LAUNCH_OK();
 }
 
 EP_API int momoe_ep_combine_rows(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
-                                 int32_t experts_per_rank, int32_t cols, void* dst, int32_t world,
+                                 int32_t experts_per_rank, int32_t cols, void* dst, int32_t world, int32_t max_blocks,
                                  momoe_stream_t stream) {
     if (home == nullptr || peer_rows == nullptr || remote_row == nullptr || dst == nullptr || home->pos_MK == nullptr ||
         home->tile_expert == nullptr)
@@ -384,7 +385,7 @@ EP_API int momoe_ep_combine_rows(const momoe_plan_t* home, void* const* peer_row
     const int vec = cols / 8;
     const long long total = static_cast<long long>(home->M) * vec;
     int blocks = static_cast<int>((total + 255) / 256);
-    const int cap = sm_count() * 16;
+    const int cap = max_blocks > 0 ? max_blocks : sm_count() * 16;
     if (blocks > cap) blocks = cap;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint4* d = static_cast<uint4*>(dst);

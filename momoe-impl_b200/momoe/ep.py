@@ -205,6 +205,8 @@ class PeerBuffers:
         self.row_gs, self.p_row_gs = alloc((cap_rows,), torch.float32)        # dL/ds of each received row
         self.counts, self.p_counts = alloc((self.world * N,), torch.int32)
         self.flags, self.p_flags = alloc((8,), torch.int32)
+        self.comm_stream = torch.cuda.Stream(device=device)
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         torch.cuda.synchronize(device)
         dist.barrier(group)     # every rank's buffers are zeroed before anybody signals
 
@@ -255,7 +257,7 @@ class PeerExpertParallelFunction(torch.autograd.Function):
             remote_row = torch.empty(home.rows_capacity, **i32)
             ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows, home.ref, ptr(x_MD), D, ptr(dst_base),
                       Nl, bufs.p_rows_x, bufs.p_row_w, ptr(remote_row), R, rank, ptr(local_count), ptr(pad_off),
-                      st())
+                      0, st())
             ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
                       ptr(status), st())
             # local experts on the received rows: already expert-major and padded
@@ -275,7 +277,7 @@ class PeerExpertParallelFunction(torch.autograd.Function):
                       ptr(status), st())
             y_MD = torch.empty((M, D), **bf)
             ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y, ptr(remote_row),
-                      Nl, D, ptr(y_MD), R, st())
+                      Nl, D, ptr(y_MD), R, 0, st())
         ctx.bufs, ctx.home, ctx.local = bufs, home, local
         ctx.keep = (dst_base, local_count, pad_off, tile_expert, pair_info, sched, remote_row)
         ctx.shape = (B, S, D)
@@ -305,10 +307,23 @@ class PeerExpertParallelFunction(torch.autograd.Function):
         status = home.status
         g_MD = G_y_BSD.reshape(M, D).to(device=dev, dtype=torch.bfloat16).contiguous()
         with torch.cuda.device(dev):
-            ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows, home.ref, ptr(g_MD), D, ptr(dst_base),
-                      Nl, bufs.p_rows_g, None, None, R, rank, ptr(local_count), ptr(pad_off), st())
-            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
-                      ptr(status), st())
+            # Two streams.  The transfers (peer stores / loads, one small block per SM) run on `comm` while grouped
+            # GEMMs that do not depend on them run on the main stream on the same SMs:
+            #   dispatch of the upstream gradient  ||  recomputation of a,b (needs only the rows kept from forward)
+            #   combine of the input gradient      ||  the two weight-gradient GEMMs
+            main = torch.cuda.current_stream()
+            comm = bufs.comm_stream
+            one_per_sm = bufs.sm_count
+            ev = [torch.cuda.Event() for _ in range(4)]
+            ev[0].record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev[0])
+                ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows, home.ref, ptr(g_MD), D,
+                          ptr(dst_base), Nl, bufs.p_rows_g, None, None, R, rank, ptr(local_count), ptr(pad_off),
+                          one_per_sm, st())
+                ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                          ptr(status), st())
+                ev[1].record(comm)
             lp = C.byref(local)
             # Tiles that do not lie entirely below the save boundary are recomputed; even at save_percent = 100 the
             # last partial tile of an expert can be one of them, so the pass always runs (it skips saved tiles).
@@ -318,28 +333,33 @@ class PeerExpertParallelFunction(torch.autograd.Function):
             b_rec = torch.empty((rec_tiles * ops.TILE_M, H), **bf)
             ops._call("momoe_up_swiglu (recompute)", 1, lib.momoe_up_swiglu, lp, ptr(bufs.rows_x), ptr(W1), None,
                       ptr(a_rec), ptr(b_rec), 2, st())
+            main.wait_event(ev[1])
             n_part = 2 * ((H + 255) // 256)
             gz = torch.empty((cap, 2 * H), **bf)
             hs = torch.empty((cap, H), **bf)
             gs_part = torch.empty((cap, n_part), dtype=torch.float32, device=dev)
             ops._call("momoe_dgrad2_swiglu_bwd", 1, lib.momoe_dgrad2_swiglu_bwd, lp, ptr(bufs.rows_g), ptr(W2),
                       ptr(a_save), ptr(b_save), ptr(a_rec), ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), st())
-            del a_rec, b_rec
+            ops._call("momoe_dgrad1", 1, lib.momoe_dgrad1, lp, ptr(gz), ptr(W1), ptr(bufs.rows_y), st())
+            ops._call("momoe_ep_reduce_gs", 1, lib.momoe_ep_reduce_gs, ptr(gs_part), n_part, ptr(sched),
+                      ptr(bufs.row_gs), st())
+            ev[2].record(main)
+            G_x = torch.empty((M, D), **bf)
+            G_s = torch.empty((N, M), dtype=torch.float32, device=dev)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev[2])
+                ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                          ptr(status), st())
+                ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y,
+                          ptr(remote_row), Nl, D, ptr(G_x), R, one_per_sm, st())
+                ops._call("momoe_ep_pull_gs", 1, lib.momoe_ep_pull_gs, home.ref, bufs.p_row_gs, ptr(remote_row), Nl,
+                          ptr(G_s), R, st())
+                ev[3].record(comm)
             G_W2 = torch.empty_like(W2)
             ops._call("momoe_wgrad (W2)", 1, lib.momoe_wgrad, lp, ptr(hs), H, ptr(bufs.rows_g), D, ptr(G_W2), st())
             G_W1 = torch.empty_like(W1)
             ops._call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, lp, ptr(bufs.rows_x), D, ptr(gz), 2 * H, ptr(G_W1), st())
-            ops._call("momoe_dgrad1", 1, lib.momoe_dgrad1, lp, ptr(gz), ptr(W1), ptr(bufs.rows_y), st())
-            ops._call("momoe_ep_reduce_gs", 1, lib.momoe_ep_reduce_gs, ptr(gs_part), n_part, ptr(sched),
-                      ptr(bufs.row_gs), st())
-            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
-                      ptr(status), st())
-            G_x = torch.empty((M, D), **bf)
-            ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y, ptr(remote_row),
-                      Nl, D, ptr(G_x), R, st())
-            G_s = torch.empty((N, M), dtype=torch.float32, device=dev)
-            ops._call("momoe_ep_pull_gs", 1, lib.momoe_ep_pull_gs, home.ref, bufs.p_row_gs, ptr(remote_row), Nl,
-                      ptr(G_s), R, st())
+            main.wait_event(ev[3])
         x_dev, s_dev = ctx.in_devices
         return (G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_s.to(s_dev), None, None, None, None, None)
 
