@@ -179,7 +179,10 @@ __global__ void ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int
         if (tok < 0) continue;
         const int e = home_tile_expert[pr / TILE_M];
         const int base = dst_base[e];
-        if (base < 0) continue;   // capacity exceeded somewhere: nothing is sent (status already records it)
+        if (base < 0) {   // capacity exceeded somewhere: nothing is sent (the status word already records it)
+            if (lane == 0 && remote_row != nullptr) remote_row[pr] = 0;   // keep later reads inside the buffers
+            continue;
+        }
         const int row = base + (pr - home_pad_off[e]);
         const int d = e / Nl;
         uint4* dst = static_cast<uint4*>(rows.p[d]) + static_cast<size_t>(row) * vec_per_row;

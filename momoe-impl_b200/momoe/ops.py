@@ -42,7 +42,8 @@ def status_word(device):
 
 _STATUS_TEXT = {101: "TMA producer wait timed out", 102: "MMA issuer wait timed out",
                 103: "epilogue wait timed out", 201: "a token does not have exactly K experts in mask_NM",
-                202: "expert id out of range"}
+                202: "expert id out of range", 301: "a peer rank did not reach a hand-shake in time",
+                302: "expert-parallel buffers too small for this routing (raise capacity_factor)"}
 
 
 def check_status(device=None):

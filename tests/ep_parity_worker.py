@@ -36,7 +36,8 @@ def run_case(transport, case, rank, world, dev, momoe, ep, ops, cos, max_rel):
     # (b) expert parallel, own shard
     moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
                                Wl1_ND2H=W1[rank * Nl:(rank + 1) * Nl].to(dev),
-                               Wl2_NHD=W2[rank * Nl:(rank + 1) * Nl].to(dev), transport=transport)
+                               Wl2_NHD=W2[rank * Nl:(rank + 1) * Nl].to(dev), transport=transport,
+                               capacity_factor=float(world))   # room for any routing, however skewed
     with torch.no_grad():
         moe.biases_N.copy_(biases.to(dev))
     xr = x_all[rank].to(dev).requires_grad_(True)
@@ -80,6 +81,23 @@ def main():
     for transport in ("peer", "nccl"):
         for case in cases:
             run_case(transport, case, rank, world, dev, momoe, ep, ops, cos, max_rel)
+    # buffers far too small for the routing: every rank must notice (device status 302) and nothing may fault
+    g = torch.Generator().manual_seed(77)
+    D, H, K = 256, 128, 2
+    N = 2 * world
+    moe = ep.ExpertParallelMoE(D, H, N, K, 0, Wg_DN=(torch.randn(D, N, generator=g) * 0.05).bfloat16().to(dev),
+                               Wl1_ND2H=torch.zeros(N // world, D, 2 * H, device=dev),
+                               Wl2_NHD=torch.zeros(N // world, H, D, device=dev), capacity_factor=0.05)
+    x = torch.randn(1, 4096, D, generator=g).bfloat16().to(dev).requires_grad_(True)
+    moe(x).sum().backward()
+    torch.cuda.synchronize()
+    try:
+        ops.check_status(dev)
+        raise AssertionError("overflow of the expert-parallel buffers was not reported")
+    except RuntimeError as err:
+        assert "302" in str(err), err
+    if rank == 0:
+        print("ep overflow reported ok", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

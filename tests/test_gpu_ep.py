@@ -19,6 +19,7 @@ def _run(world):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("ep parity ok") == 6   # 3 cases x 2 transports
+    assert "ep overflow reported ok" in res.stdout
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
