@@ -244,9 +244,9 @@ def main():
     # DRAM bytes per launch (read + write) from the ncu capture summarised in
     # profiles/grouped_gemm_reduced_case_ncu_full.md (32 experts, 4096 tokens), per (expert x token) unit; traffic
     # grows in proportion to both, so it is scaled to this run's experts and tokens.
-    ncu_mb_small = {"momoe_up_swiglu": 471, "momoe_up_swiglu (recompute)": 537, "momoe_down_scale": 309,
-                    "momoe_dgrad2_swiglu_bwd": 600, "momoe_wgrad (W2)": 316, "momoe_wgrad (W1)": 511,
-                    "momoe_dgrad1": 532}
+    ncu_mb_small = {"momoe_up_swiglu": 474, "momoe_up_swiglu (recompute)": 535, "momoe_down_scale": 316,
+                    "momoe_dgrad2_swiglu_bwd": 611, "momoe_wgrad (W2)": 319, "momoe_wgrad (W1)": 519,
+                    "momoe_dgrad1": 534}
     traffic_scale = 0.5 * (N / 32.0 + M / 4096.0)
     peaks = measured_peaks()
     kernels = []
