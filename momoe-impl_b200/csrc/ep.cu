@@ -168,12 +168,12 @@ __global__ void ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int
                                         const int* __restrict__ home_sched, const float* __restrict__ home_row_weight,
                                         const int* __restrict__ dst_base, int Nl, int vec_per_row, PeerPtrs rows,
                                         PeerPtrs row_w, int* __restrict__ remote_row, int rank,
-                                        const int* __restrict__ local_count, const int* __restrict__ local_pad_off) {
+                                        const int* __restrict__ local_count, const int* __restrict__ local_pad_off,
+                                        bool wide) {
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
     const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int home_rows = home_sched[SCHED_PAD_ROWS];
-    const bool wide = (vec_per_row & 1) == 0;   // rows start on 32-byte boundaries
     for (int pr = wid; pr < home_rows; pr += warps_total) {
         const int tok = home_row_token[pr];
         if (tok < 0) continue;
@@ -369,9 +369,13 @@ EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int
     if (fill_peers(r, peer_rows, world) != MOMOE_OK || fill_peers(w, peer_row_weight, world) != MOMOE_OK)
         return MOMOE_ERR_ARG;
     const int grid = max_blocks > 0 ? max_blocks : sm_count() * 8;
+    uintptr_t align = reinterpret_cast<uintptr_t>(src);
+    for (int i = 0; i < world; ++i) align |= reinterpret_cast<uintptr_t>(r.p[i]);
+    const bool wide = (cols % 16 == 0) && (align & 31) == 0;   // 256-bit stores need 32-byte aligned rows
     ep_dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(src), home->row_token, home->tile_expert, home->pad_off, home->sched,
-        home->row_weight, dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, local_count, local_pad_off);
+        home->row_weight, dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, local_count, local_pad_off,
+        wide);
     return EP_LAUNCH_OK();
 }
 
