@@ -25,7 +25,10 @@ for _p in (ROOT, os.path.join(ROOT, "momoe-impl_b200")):
 import torch  # noqa: E402
 
 METRIC = "MoE layer fwd+bwd tokens/sec (D2048 H1024 N128 K8 bf16)"
-CFG = dict(D=2048, H=1024, N=128, K=8, Ks=0, B=8, S=2048)
+CFG = dict(D=2048, H=1024, N=128, K=8, Ks=0, B=8, S=2048, w_std=0.02, zipf=False)
+# Optional second workload (--workload large_ep): the large expert-parallel layer, 65536 tokens per GPU, router biased
+# with a Zipf(1.1) profile so that the busiest expert receives about 8x the mean.  Not the headline metric.
+LARGE_EP = dict(D=7168, H=2048, N=256, K=8, Ks=0, B=32, S=2048, w_std=0.006, zipf=True)
 CPU_SAMPLE_TOKENS = 2048
 
 
@@ -88,11 +91,36 @@ class ClockSampler:
 def make_weights(seed, N, D, H, device, n_total, std=0.02):
     g = torch.Generator(device="cpu").manual_seed(seed)
     Wg = (torch.randn(D, n_total, generator=g) * std).bfloat16()
-    # expert weights are generated on the device to avoid shipping gigabytes through the host
+    # expert weights are generated on the device, a few experts at a time (the fp32 draw of a whole tensor would
+    # double its footprint)
     gd = torch.Generator(device=device).manual_seed(seed + 1)
-    W1 = (torch.randn(N, D, 2 * H, generator=gd, device=device) * std).bfloat16()
-    W2 = (torch.randn(N, H, D, generator=gd, device=device) * std).bfloat16()
+    W1 = torch.empty((N, D, 2 * H), dtype=torch.bfloat16, device=device)
+    W2 = torch.empty((N, H, D), dtype=torch.bfloat16, device=device)
+    for e0 in range(0, N, 16):
+        e1 = min(N, e0 + 16)
+        W1[e0:e1] = (torch.randn(e1 - e0, D, 2 * H, generator=gd, device=device) * std).bfloat16()
+        W2[e0:e1] = (torch.randn(e1 - e0, H, D, generator=gd, device=device) * std).bfloat16()
     return Wg.to(device), W1, W2
+
+
+def zipf_biases(x_MD, Wg, N, K, target=8.0, seed=7):
+    """Router biases b_e = -alpha * 1.1 * ln(rank_e), rank = seeded permutation of 1..N, alpha by bisection so that
+    the busiest expert gets `target` x the mean number of tokens on these inputs."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    rank_e = (torch.randperm(N, generator=g) + 1).float().to(x_MD.device)
+    shape = -1.1 * torch.log(rank_e)
+    p = torch.softmax((x_MD @ Wg).float(), dim=-1)
+    lo, hi = 0.0, 1.0
+    for _ in range(24):
+        mid = 0.5 * (lo + hi)
+        sel = torch.topk(p + mid * shape[None, :], K, dim=-1).indices
+        counts = torch.bincount(sel.reshape(-1), minlength=N).float()
+        ratio = float(counts.max() / counts.mean())
+        if ratio < target:
+            lo = mid
+        else:
+            hi = mid
+    return (0.5 * (lo + hi)) * shape
 
 
 def cpu_sample(steps, warmup, seed=0):
@@ -146,6 +174,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory leg (profiling runs)")
     ap.add_argument("--experts", type=int, default=CFG["N"], help="reduced case for profiler captures")
     ap.add_argument("--tokens", type=int, default=CFG["B"] * CFG["S"], help="reduced case for profiler captures")
+    ap.add_argument("--workload", default="headline", choices=["headline", "large_ep"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -169,20 +198,20 @@ def main():
     import momoe
     from momoe import ops
 
-    c = dict(CFG)
-    reduced = args.experts != c["N"] or args.tokens != c["B"] * c["S"]
+    c = dict(CFG if args.workload == "headline" else LARGE_EP)
+    reduced = args.workload == "headline" and (args.experts != c["N"] or args.tokens != c["B"] * c["S"])
     if reduced:
         c.update(N=args.experts, B=1, S=args.tokens)
     D, H, N, K, Ks = c["D"], c["H"], c["N"], c["K"], c["Ks"]
     M = c["B"] * c["S"]
     if world > 1:
         from momoe import ep
-        Wg, W1, W2 = make_weights(1234, N // world, D, H, dev, N)          # this rank's expert block
+        Wg, W1, W2 = make_weights(1234, N // world, D, H, dev, N, c["w_std"])   # this rank's expert block
         moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=args.save_percent, Wg_DN=Wg, Wl1_ND2H=W1,
                                    Wl2_NHD=W2, group=dist.group.WORLD)
         parallelism = "ep%d" % world
     else:
-        Wg, W1, W2 = make_weights(1234, N, D, H, dev, N)
+        Wg, W1, W2 = make_weights(1234, N, D, H, dev, N, c["w_std"])
         moe = momoe.MoE(D, H, N, K, Ks, save_percent=args.save_percent, Wg_DN=Wg, Wl1_ND2H=W1, Wl2_NHD=W2)
         parallelism = "single"
     del W1, W2
@@ -190,6 +219,12 @@ def main():
     x_host = torch.randn(c["B"], c["S"], D, generator=gen).bfloat16().pin_memory()
     g_dev = torch.randn(c["B"], c["S"], D, generator=gen).bfloat16().to(dev)
     x_dev = x_host.to(dev).requires_grad_(True)
+    if c["zipf"]:
+        b = zipf_biases(x_dev.detach().reshape(M, D), Wg, N, K)
+        if world > 1:
+            dist.broadcast(b, 0)      # every rank routes with rank 0's bias profile
+        with torch.no_grad():
+            moe.biases_N.copy_(b)
 
     def zero_grads():
         for p in moe.parameters():
@@ -263,7 +298,8 @@ def main():
         top = gemms[0]
         roofline = dict(bound="tensor", kernel="grouped_gemm_kernel / " + top["name"], achieved=top["tflops"],
                         peak=peaks["tflops"], unit="TFLOP/s", frac=round(top["tflops"] / peaks["tflops"], 4),
-                        traffic=ncu_mb_small[top["name"]] * 1e6 * traffic_scale, peak_source=peaks["source"],
+                        traffic=(ncu_mb_small[top["name"]] * 1e6 * traffic_scale) if args.workload == "headline" else None,
+                        peak_source=peaks["source"],
                         traffic_note="dram__bytes_read+write per launch from an ncu capture of a 1/4-size case, scaled",
                         flops_per_launch=flops[top["name"]] * unit_flops, ms_per_launch=top["ms"])
     layer_flops = (18.0 * K * D * H + 6.0 * D * N) * M   # algorithmic fwd+bwd flops per rank and step
@@ -297,15 +333,20 @@ def main():
     ops.check_status(dev)
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "headline":
         cb = cpu_sample(2, 1)
         cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
     if rank == 0:
         line = dict(
-            metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+            metric=METRIC if args.workload == "headline" else
+            "MoE layer fwd+bwd tokens/sec (D%d H%d N%d K%d bf16)" % (D, H, N, K),
+            value=value, unit="tokens/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
             config=dict(workload=("REDUCED profiling case N%d tokens %d (not the headline workload)" % (N, M)) if reduced
+                        else ("large expert-parallel layer: D7168 H2048 N256 K8, 65536 tokens per GPU, Zipf(1.1) router "
+                              "bias (busiest expert 8x mean), fwd+bwd (not the headline workload)")
+                        if args.workload == "large_ep"
                         else "cfg2 headline layer: D2048 H1024 N128 K8, B8 S2048 (16384 tokens) per GPU, fwd+bwd",
                         tokens_per_gpu=M, save_percent=args.save_percent, parallelism=parallelism,
                         l2="inputs larger than L2 (weights 1.6 GB, activations > 0.5 GB per step)"),

@@ -159,6 +159,11 @@ int momoe_router_backward(const float* G_s, int64_t gs_stride_n, int64_t gs_stri
                           const float* s_MN, const float* Ng_M, const float* Ks_M, const int32_t* mask_NM,
                           int32_t M, int32_t N, int32_t Ks, void* G_logits_MN, momoe_stream_t stream);
 
+/* Aux-loss-free load balancing in place: biases_N[e] += rate * sign(c_avg - sizes_N[e]) for e < N-Ks, in fp32 (the
+ * shared experts' entries, -inf, are not touched).  Replaces the three torch ops of momoe/sample_moe.py:64-66. */
+int momoe_bias_update(float* biases_N, const int64_t* sizes_N, int32_t N, int32_t Ks, float c_avg, float rate,
+                      momoe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Expert parallelism over peer memory (no counterpart in the reference, whose README lists expert parallelism as
  * unsupported).  R <= 8 ranks of one NVLink node, one process per GPU; rank r owns experts [r*N/R, (r+1)*N/R).

@@ -472,6 +472,16 @@ __global__ void router_backward_kernel(const float* __restrict__ G_s, long long 
     }
 }
 
+// Aux-loss-free balancing: b[e] += rate * sign(c_avg - tokens[e]) for the gating experts (shared experts keep -inf).
+__global__ void bias_update_kernel(float* __restrict__ biases, const long long* __restrict__ sizes, int n_gating,
+                                   float c_avg, float rate) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n_gating) return;
+    const float d = c_avg - static_cast<float>(sizes[e]);
+    const float sg = d > 0.0f ? 1.0f : (d < 0.0f ? -1.0f : 0.0f);
+    biases[e] += rate * sg;
+}
+
 static inline int cdiv(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
 
 }  // namespace momoe
@@ -619,6 +629,15 @@ extern "C" __attribute__((visibility("default"))) int momoe_scatter_gs(const mom
         return MOMOE_ERR_CUDA;
     scatter_gs_kernel<<<sm_count() * 4, 256, 0, st>>>(gs_part, n_part, plan->row_token, plan->tile_expert, plan->sched,
                                                       plan->M, G_s_NM);
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_bias_update(float* biases_N, const int64_t* sizes_N,
+                                                                         int32_t N, int32_t Ks, float c_avg,
+                                                                         float rate, momoe_stream_t stream) {
+    if (biases_N == nullptr || sizes_N == nullptr || N <= 0 || Ks < 0 || Ks >= N) return MOMOE_ERR_ARG;
+    bias_update_kernel<<<cdiv(N - Ks, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        biases_N, reinterpret_cast<const long long*>(sizes_N), N - Ks, c_avg, rate);
     return LAUNCH_OK();
 }
 

@@ -21,6 +21,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from . import ops
 from .topk_router import TopKRouter
 
 
@@ -414,8 +415,35 @@ class ExpertParallelMoE(nn.Module):
                                                           topk_w, self.K, self.save_percent, self.group)
         R = dist.get_world_size(self.group)
         c_avg = B * S * R * (self.K - self.Ks) / (self.N - self.Ks)
-        self.biases_N += self.bias_update_rate * torch.sign(c_avg - sizes_N.to(self.biases_N.device))
+        with torch.no_grad():
+            ops.bias_update_(self.biases_N.data, sizes_N, self.Ks, c_avg, self.bias_update_rate)
         return y_BSD
+
+    # ---- checkpoints in the single-GPU layout (keys router.Wg_DN, momoe.Wl1_ND2H, momoe.Wl2_NHD, biases_N)
+    def load_full_state_dict(self, state):
+        """Load a checkpoint of the single-GPU `MoE` layer: every rank keeps its own block of experts."""
+        R, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        Nl = self.N // R
+        with torch.no_grad():
+            self.router.Wg_DN.copy_(state["router.Wg_DN"])
+            self.biases_N.copy_(state["biases_N"])
+            self.Wl1_ND2H.copy_(state["momoe.Wl1_ND2H"][rank * Nl:(rank + 1) * Nl])
+            self.Wl2_NHD.copy_(state["momoe.Wl2_NHD"][rank * Nl:(rank + 1) * Nl])
+
+    def full_state_dict(self):
+        """The layer's parameters in the single-GPU layout, on every rank (expert blocks are all-gathered)."""
+        R = dist.get_world_size(self.group)
+
+        def gather(w):
+            w = w.detach().contiguous()
+            out = torch.empty((R,) + tuple(w.shape), dtype=w.dtype, device=w.device)
+            # raw bytes: every backend moves uint8
+            dist.all_gather_into_tensor(out.view(torch.uint8).reshape(-1), w.view(torch.uint8).reshape(-1),
+                                        group=self.group)
+            return out.reshape((R * w.shape[0],) + tuple(w.shape[1:]))
+
+        return {"router.Wg_DN": self.router.Wg_DN.detach().clone(), "biases_N": self.biases_N.detach().clone(),
+                "momoe.Wl1_ND2H": gather(self.Wl1_ND2H), "momoe.Wl2_NHD": gather(self.Wl2_NHD)}
 
     def _peer_buffers(self, M):
         """Symmetric buffers sized for `capacity_factor` times the average number of rows a rank receives (plus one

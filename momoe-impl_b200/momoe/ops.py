@@ -230,3 +230,11 @@ def router_backward(G_s_NM, s_postsoft_MN, s_MN, Ng_M, Ks_M, mask_NM, Ks):
     _call("momoe_router_backward", 1, lib.momoe_router_backward, ptr(G_s_NM), G_s_NM.stride(0), G_s_NM.stride(1), ptr(s_postsoft_MN), ptr(s_MN),
                                     ptr(Ng_M), ptr(Ks_M), ptr(mask_NM), M, N, Ks, ptr(out), stream_ptr())
     return out
+
+
+def bias_update_(biases_N, sizes_N, Ks, c_avg, rate):
+    """In-place aux-loss-free bias update (one kernel instead of the reference's three torch ops)."""
+    N = biases_N.shape[0]
+    sizes_N = sizes_N.to(device=biases_N.device, dtype=torch.int64)
+    _call("momoe_bias_update", 1, lib.momoe_bias_update, ptr(biases_N), ptr(sizes_N), N, Ks, float(c_avg), float(rate),
+          stream_ptr())

@@ -3,6 +3,7 @@
 import torch
 import torch.nn as nn
 
+from . import ops
 from .momoe import MoMoE
 from .topk_router import TopKRouter
 
@@ -36,5 +37,6 @@ class MoE(nn.Module):
         # DeepSeek-style auxiliary-loss-free balancing: push the bias of under-loaded experts up
         B, S, _ = x_BSD.shape
         c_avg = B * S * (self.K - self.Ks) / (self.N - self.Ks)
-        self.biases_N += self.bias_update_rate * torch.sign(c_avg - sizes_N.to(self.biases_N.device))
+        with torch.no_grad():
+            ops.bias_update_(self.biases_N.data, sizes_N, self.Ks, c_avg, self.bias_update_rate)
         return y_BSD
