@@ -163,13 +163,57 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_triton_reference(args):
+    """Context only (not part of the measurement contract): the UNMODIFIED reference package, installed with pip into
+    baseline/_ref, on the same GPU, same layer, same timing protocol.  Its Triton kernels autotune during warm-up."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "momoe")):
+        print(json.dumps({"impl": "reference-triton", "unavailable": "baseline/_ref is not installed"}))
+        return
+    sys.path[:] = [ref_dir] + [p for p in sys.path if os.path.join(ROOT, "momoe-impl_b200") != p]
+    import momoe as ref   # the reference package
+    assert os.path.dirname(ref.__file__).startswith(ref_dir)
+    c = CFG
+    D, H, N, K, Ks = c["D"], c["H"], c["N"], c["K"], c["Ks"]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Wg, W1, W2 = make_weights(1234, N, D, H, dev, N, c["w_std"])
+    moe = ref.MoE(D, H, N, K, Ks, save_percent=args.save_percent, Wg_DN=Wg, Wl1_ND2H=W1, Wl2_NHD=W2)
+    del W1, W2
+    gen = torch.Generator(device="cpu").manual_seed(100)
+    x = torch.randn(c["B"], c["S"], D, generator=gen).bfloat16().to(dev).requires_grad_(True)
+    g = torch.randn(c["B"], c["S"], D, generator=gen).bfloat16().to(dev)
+
+    def step():
+        for p in moe.parameters():
+            p.grad = None
+        x.grad = None
+        moe(x).backward(g)
+
+    for _ in range(max(args.warmup, 12)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    M = c["B"] * c["S"]
+    print(json.dumps(dict(metric=METRIC, impl="reference-triton", value=M / (ms * 1e-3), unit="tokens/s", n_gpus=1,
+                          steps=args.steps, ms_per_step=ms, dtype="bf16", data="synthetic",
+                          config=dict(workload="cfg2 headline layer, reference package from baseline/_ref",
+                                      save_percent=args.save_percent))), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--save-percent", type=float, default=0.0)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory leg (profiling runs)")
     ap.add_argument("--experts", type=int, default=CFG["N"], help="reduced case for profiler captures")
@@ -183,6 +227,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.impl == "reference-triton":
+        if rank == 0:
+            run_triton_reference(args)
         return
 
     import torch.distributed as dist
