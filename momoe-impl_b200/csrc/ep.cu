@@ -188,7 +188,19 @@ __global__ void ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int
         uint4* dst = static_cast<uint4*>(rows.p[d]) + static_cast<size_t>(row) * vec_per_row;
         const uint4* s = src + static_cast<size_t>(tok) * vec_per_row;
         if (wide) {
-            for (int c = lane * 2; c < vec_per_row; c += 64) st_256(dst + c, __ldg(s + c), __ldg(s + c + 1));
+            // all loads of a batch first, then the (posted) peer stores: four 32-byte pieces per lane in flight
+            for (int c0 = lane * 2; c0 < vec_per_row; c0 += 256) {
+                uint4 t[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (c0 + j * 64 < vec_per_row) {
+                        t[2 * j] = __ldg(s + c0 + j * 64);
+                        t[2 * j + 1] = __ldg(s + c0 + j * 64 + 1);
+                    }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (c0 + j * 64 < vec_per_row) st_256(dst + c0 + j * 64, t[2 * j], t[2 * j + 1]);
+            }
         } else {
             for (int c = lane; c < vec_per_row; c += 32) dst[c] = __ldg(s + c);
         }

@@ -1,6 +1,7 @@
 """Host-side plumbing above the C ABI: device buffers (torch), the routing plan, and the forward / backward
 sequences of kernel launches.  No arithmetic on tensor contents happens here."""
 import ctypes as C
+import os
 
 import torch
 
@@ -14,6 +15,7 @@ _status_words = {}
 # is bracketed by CUDA events on the launching stream (used by the benchmark for per-kernel device times).
 LAUNCHES = 0
 KERNEL_EVENTS = None
+NVTX = os.environ.get("MOMOE_B200_NVTX", "0") == "1"   # one NVTX range per C-ABI call, for timeline tools
 
 
 def _call(name, n_kernels, fn, *args):
@@ -26,6 +28,10 @@ def _call(name, n_kernels, fn, *args):
         rc = fn(*args)
         e1.record()
         ev.append((name, e0, e1))
+    elif NVTX:
+        torch.cuda.nvtx.range_push(name)
+        rc = fn(*args)
+        torch.cuda.nvtx.range_pop()
     else:
         rc = fn(*args)
     check(rc, name)

@@ -153,3 +153,31 @@ def test_forward_is_deterministic_and_training_reduces_loss(momoe):
         losses.append(float(loss))
     _check_status()
     assert losses[-1] < losses[0] * 0.9, losses
+
+
+def test_memory_held_for_backward_follows_save_percent(momoe):
+    """What the layer keeps alive between forward and backward: the bf16 input, the routing tables and, for the saved
+    share of the rows only, the pre-activations a and b (2 * rows * H * 2 bytes).  Nothing else (no [K,M,D] slab, no
+    y_pre): the reference's memory chart property."""
+    B, S, D, H, N, K = 4, 2048, 1024, 512, 32, 4
+    M, Msum = B * S, B * S * K
+    g = torch.Generator().manual_seed(0)
+    W1 = (torch.randn(N, D, 2 * H, generator=g) * 0.02).bfloat16().cuda()
+    W2 = (torch.randn(N, H, D, generator=g) * 0.02).bfloat16().cuda()
+    Wg = (torch.randn(D, N, generator=g) * 0.02).bfloat16().cuda()
+    x = torch.randn(B, S, D, generator=g).bfloat16().cuda().requires_grad_(True)
+    held = {}
+    for sp in (0, 50, 100):
+        moe = momoe.MoE(D, H, N, K, 0, save_percent=sp, Wg_DN=Wg, Wl1_ND2H=W1, Wl2_NHD=W2)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        before = torch.cuda.memory_allocated()
+        y = moe(x)
+        torch.cuda.synchronize()
+        held[sp] = torch.cuda.memory_allocated() - before - y.numel() * 2
+        y.sum().backward()
+        del y, moe
+    ab_all = 2 * Msum * H * 2
+    assert held[0] < 0.35 * ab_all                      # tables + weights cast + router state only
+    assert 0.4 * ab_all < held[50] - held[0] < 0.75 * ab_all
+    assert 0.9 * ab_all < held[100] - held[0] < 1.35 * ab_all
