@@ -1,11 +1,18 @@
 """`MoMoE`: the memory-optimised SwiGLU mixture-of-experts layer, same constructor, parameters and
 `(y_BSD, tokens_per_expert_N)` contract as the reference module (momoe/momoe.py:914-972 there), running on
 hand-written sm_100a kernels through libmomoe_b200.so."""
+import os
+
 import torch
 import torch.nn as nn
 
 from . import ops
 from ._lib import require_cuda
+
+
+# MOMOE_B200_CHECK=1: synchronise after every forward / backward and raise if a kernel reported a device-side problem
+# (a token without exactly K experts, a wait that ran out).  Off by default: the layer never synchronises the host.
+_CHECK = os.environ.get("MOMOE_B200_CHECK", "0") == "1"
 
 
 class MoEFunction(torch.autograd.Function):
@@ -39,6 +46,8 @@ class MoEFunction(torch.autograd.Function):
             saved += [a_save, b_save]
         ctx.save_for_backward(*saved)
         ctx.mark_non_differentiable(plan.sizes)
+        if _CHECK:
+            ops.check_status(dev)
         return y_MD.reshape(B, S, D).to(device=x_BSD.device), plan.sizes
 
     @staticmethod
@@ -52,6 +61,8 @@ class MoEFunction(torch.autograd.Function):
         g_MD = G_y_BSD.reshape(B * S, D).to(device=dev, dtype=torch.bfloat16).contiguous()
         with torch.cuda.device(dev):
             G_x, G_W1, G_W2, G_s = ops.experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save)
+        if _CHECK:
+            ops.check_status(dev)
         x_dev, s_dev = ctx.in_devices
         return G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_s.to(s_dev), None, None
 
