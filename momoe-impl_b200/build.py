@@ -33,13 +33,17 @@ def build(out=LIB_PATH, extra_flags=(), force=False, verbose=False):
     deps.append(os.path.join(HERE, "..", "include", "momoe_b200.h"))
     if not force and not _stale(out, deps):
         return out
-    cmd = [nvcc, "-shared", "-o", out] + NVCC_FLAGS + list(extra_flags) + srcs
+    tmp = out + ".tmp%d" % os.getpid()     # written beside the target, then renamed: readers never see a partial file
+    cmd = [nvcc, "-shared", "-o", tmp] + NVCC_FLAGS + list(extra_flags) + srcs
     if verbose:
         print(" ".join(cmd))
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed building " + out)
+    os.replace(tmp, out)
     if verbose:
         sys.stderr.write(res.stdout + res.stderr)
     return out
