@@ -207,6 +207,81 @@ def run_triton_reference(args):
                                       save_percent=args.save_percent))), flush=True)
 
 
+INFER = dict(D=2048, H=768, N=128, K=8, tokens=(1, 8, 64, 256, 4096, 16384), w_std=0.02)
+
+
+def run_inference(args, dev):
+    """--workload inference: forward-only latency of the 30B-A3B-class layer (D2048 H768 N128 K8) through the
+    `MoMoE` module for batches of 1..16384 tokens, router logits N(0,1) + expert bias N(0,0.5).  Each batch is timed
+    eagerly (host launches included) and as a replayed CUDA graph of the same calls; the HBM figure is the bytes
+    every touched expert's weights occupy (3*D*H*2 per expert) plus the token rows moved, over the graph time."""
+    import momoe
+    from momoe import ops
+    c = INFER
+    D, H, N, K = c["D"], c["H"], c["N"], c["K"]
+    peaks = measured_peaks()
+    Wg, W1, W2 = make_weights(1234, N, D, H, dev, N, c["w_std"])
+    layer = momoe.MoMoE(D, H, N, K, save_percent=0, Wl1_ND2H=W1, Wl2_NHD=W2)
+    del W1, W2
+    gen = torch.Generator(device=dev).manual_seed(5)
+    e_bias = 0.5 * torch.randn(N, generator=gen, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # larger than L2
+    points = []
+    for T in c["tokens"]:
+        x = torch.randn(1, T, D, generator=gen, device=dev).bfloat16()
+        logits = (torch.randn(T, N, generator=gen, device=dev) + e_bias).bfloat16()
+        zeros = torch.zeros(N, device=dev)
+
+        def fwd():
+            with torch.no_grad():
+                idx, w, _ = ops.route_topk(logits, zeros, K, 0, dense=False)
+                plan = ops.RoutingPlan.from_topk(idx, w, N, D, H, 0)
+                y, _, _ = ops.experts_forward(plan, x, layer.Wl1_ND2H.detach(), layer.Wl2_NHD.detach())
+            return y, plan.sizes
+
+        for _ in range(3):
+            y, sizes = fwd()
+        torch.cuda.synchronize()
+        ops.check_status()
+        touched = int((sizes > 0).sum())
+        l0 = ops.LAUNCHES
+        fwd()
+        launches = ops.LAUNCHES - l0
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fwd()
+
+        def timed(fn):
+            ts = []
+            for _ in range(max(args.steps, 5)):
+                flush.zero_()
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            return statistics.median(ts)
+
+        t_eager = timed(fwd)
+        t_graph = timed(graph.replay)
+        ops.check_status()
+        nbytes = touched * 3 * D * H * 2 + T * D * 2 * 2 + T * K * (2 * D + 2 * H) * 2
+        flops = 6.0 * T * K * D * H
+        points.append(dict(tokens=T, experts_touched=touched, launches=launches, ms_eager=round(t_eager, 4),
+                           ms_graph=round(t_graph, 4), hbm_gbs=round(nbytes / t_graph / 1e6, 1),
+                           hbm_frac=round(nbytes / t_graph / 1e6 / peaks["hbm"], 3),
+                           tflops=round(flops / t_graph / 1e9, 1),
+                           tokens_per_s=round(T / t_graph * 1e3, 1)))
+        del graph
+    print(json.dumps(dict(metric="MoE layer forward latency per token batch (D2048 H768 N128 K8 bf16)", unit="ms",
+                          higher_is_better=False, n_gpus=1, dtype="bf16", data="synthetic",
+                          config=dict(workload="inference forward, token batches 1..16384, L2 flushed between "
+                                               "iterations; not the headline workload"),
+                          peak_hbm_gbs=peaks["hbm"], peak_source=peaks["source"], points=points)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -218,7 +293,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory leg (profiling runs)")
     ap.add_argument("--experts", type=int, default=CFG["N"], help="reduced case for profiler captures")
     ap.add_argument("--tokens", type=int, default=CFG["B"] * CFG["S"], help="reduced case for profiler captures")
-    ap.add_argument("--workload", default="headline", choices=["headline", "large_ep"])
+    ap.add_argument("--workload", default="headline", choices=["headline", "large_ep", "inference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -245,6 +320,11 @@ def main():
         dist.barrier()
     import momoe
     from momoe import ops
+
+    if args.workload == "inference":
+        if rank == 0:
+            run_inference(args, dev)
+        return
 
     c = dict(CFG if args.workload == "headline" else LARGE_EP)
     reduced = args.workload == "headline" and (args.experts != c["N"] or args.tokens != c["B"] * c["S"])

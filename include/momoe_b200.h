@@ -61,7 +61,9 @@ int64_t momoe_tile_capacity(int32_t M, int32_t K, int32_t N);
  *   logits_MN   bf16 [M,N] contiguous;  biases_N fp32 [N] (entries of shared experts are not read)
  *   topk_idx_MK int32 [M,K] ascending expert ids (shared experts last);  topk_w_MK fp32 [M,K] their weights
  *   optional dense outputs (all NULL or all non-NULL): mask_NM int32 [N,M], s_MN fp32 [M,N] (the reference's
- *   s_NM is its transpose view), s_postsoft_MN fp32 [M,N], Ng_M fp32 [M], Ks_M fp32 [M]. */
+ *   s_NM is its transpose view), s_postsoft_MN fp32 [M,N];
+ *   optional normalisers (both NULL or both non-NULL; required with the dense outputs): Ng_M fp32 [M] = sum of the
+ *   selected gating probabilities, Ks_M fp32 [M] = sum of the shared experts' probabilities. */
 int momoe_route_topk(const void* logits_MN, const float* biases_N, int32_t M, int32_t N, int32_t K, int32_t Ks,
                      int32_t* topk_idx_MK, float* topk_w_MK, int32_t* mask_NM, float* s_MN, float* s_postsoft_MN,
                      float* Ng_M, float* Ks_M, momoe_stream_t stream);
@@ -158,6 +160,14 @@ int momoe_scatter_gs(const momoe_plan_t* plan, const float* gs_part, int32_t n_p
 int momoe_router_backward(const float* G_s, int64_t gs_stride_n, int64_t gs_stride_m, const float* s_postsoft_MN,
                           const float* s_MN, const float* Ng_M, const float* Ks_M, const int32_t* mask_NM,
                           int32_t M, int32_t N, int32_t Ks, void* G_logits_MN, momoe_stream_t stream);
+
+/* The same router backward without any dense [N,M] tensor: reads the per-row partial sums that
+ * momoe_dgrad2_swiglu_bwd wrote (summed in the order momoe_scatter_gs uses), the compact routing of
+ * momoe_route_topk and its two normalisers; unselected experts get a zero gradient.  Output G_logits_MN bf16 [M,N].
+ * Replaces momoe/momoe.py:721,699-703 (dense G_s) together with momoe/topk_router.py:11-56.  K <= 32. */
+int momoe_router_backward_compact(const momoe_plan_t* plan, const float* gs_part, int32_t n_part,
+                                  const int32_t* topk_idx_MK, const float* topk_w_MK, const float* Ng_M,
+                                  const float* Ks_M, int32_t Ks, void* G_logits_MN, momoe_stream_t stream);
 
 /* Aux-loss-free load balancing in place: biases_N[e] += rate * sign(c_avg - sizes_N[e]) for e < N-Ks, in fp32 (the
  * shared experts' entries, -inf, are not touched).  Replaces the three torch ops of momoe/sample_moe.py:64-66. */

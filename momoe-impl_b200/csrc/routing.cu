@@ -148,10 +148,10 @@ __global__ void route_topk_kernel(const __nv_bfloat16* __restrict__ logits, cons
             s_postsoft_MN[static_cast<size_t>(m) * N + Ng + lane] = ps;
             mask_NM[static_cast<size_t>(Ng + lane) * M + m] = 1;
         }
-        if (lane == 0) {
-            Ng_M[m] = ng;
-            Ks_M[m] = ks_sum;
-        }
+    }
+    if (Ng_M != nullptr && lane == 0) {
+        Ng_M[m] = ng;
+        Ks_M[m] = ks_sum;
     }
 }
 
@@ -472,6 +472,42 @@ __global__ void router_backward_kernel(const float* __restrict__ G_s, long long 
     }
 }
 
+// Router backward from the per-row partial sums of the experts' backward pass, without any dense [N,M] tensor.
+// One warp per token, lane k owns the token's k-th selected expert.  Same formulas as router_backward_kernel; the
+// unnormalised probability of a selected expert is its routing weight times the group's normaliser, and every
+// unselected expert has a zero gradient because its masked probability is zero (momoe/topk_router.py:11-56).
+__global__ void router_backward_compact_kernel(const float* __restrict__ gs_part, int n_part,
+                                               const int* __restrict__ pos_MK, const int* __restrict__ topk_idx,
+                                               const float* __restrict__ topk_w, const float* __restrict__ Ng_M,
+                                               const float* __restrict__ Ks_M, int M, int N, int K, int Ks,
+                                               __nv_bfloat16* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (m >= M) return;
+    const int Kg = K - Ks;
+    __nv_bfloat16* orow = out + static_cast<size_t>(m) * N;
+    for (int j = lane; j < N; j += 32) orow[j] = __float2bfloat16_rn(0.0f);
+    __syncwarp();
+    float g = 0.0f, w = 0.0f;
+    int e = 0;
+    if (lane < K) {
+        const size_t r = static_cast<size_t>(pos_MK[static_cast<size_t>(m) * K + lane]) * n_part;
+        for (int p = 0; p < n_part; ++p) g += gs_part[r + p];
+        w = topk_w[static_cast<size_t>(m) * K + lane];
+        e = topk_idx[static_cast<size_t>(m) * K + lane];
+    }
+    const bool gating = lane < Kg;
+    const bool shared = lane >= Kg && lane < K;
+    const float dot_g = warp_sum(gating ? g * w : 0.0f);
+    const float dot_s = warp_sum(shared ? g * w : 0.0f);
+    const float norm = gating ? Ng_M[m] : (shared ? Ks_M[m] : 1.0f);
+    const float u = (g - (gating ? dot_g : dot_s)) * (1.0f / norm);
+    const float q = w * norm;
+    const float t_g = warp_sum(gating ? u * q : 0.0f);
+    const float t_s = warp_sum(shared ? u * q : 0.0f);
+    if (lane < K) orow[e] = __float2bfloat16_rn(q * (u - (gating ? t_g : t_s)));
+}
+
 // Aux-loss-free balancing: b[e] += rate * sign(c_avg - tokens[e]) for the gating experts (shared experts keep -inf).
 __global__ void bias_update_kernel(float* __restrict__ biases, const long long* __restrict__ sizes, int n_gating,
                                    float c_avg, float rate) {
@@ -498,9 +534,8 @@ extern "C" __attribute__((visibility("default"))) int momoe_route_topk(const voi
     if (M <= 0 || N <= 0 || K <= 0 || Ks < 0 || Ks >= K || K - Ks > N - Ks) return MOMOE_ERR_ARG;
     if (N > MAX_EXPERTS || K > MAX_TOPK || Ks > 32) return MOMOE_ERR_TOO_LARGE;
     const bool dense = mask_NM != nullptr;
-    if (dense != (s_MN != nullptr) || dense != (s_postsoft_MN != nullptr) || dense != (Ng_M != nullptr) ||
-        dense != (Ks_M != nullptr))
-        return MOMOE_ERR_ARG;
+    if (dense != (s_MN != nullptr) || dense != (s_postsoft_MN != nullptr)) return MOMOE_ERR_ARG;
+    if ((Ng_M != nullptr) != (Ks_M != nullptr) || (dense && Ng_M == nullptr)) return MOMOE_ERR_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dense) {
         if (cudaMemsetAsync(mask_NM, 0, sizeof(int32_t) * static_cast<size_t>(N) * M, st) != cudaSuccess)
@@ -652,6 +687,21 @@ extern "C" __attribute__((visibility("default"))) int momoe_router_backward(cons
     const int warps = 8;
     router_backward_kernel<<<cdiv(M, warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         G_s, gs_stride_n, gs_stride_m, s_postsoft_MN, s_MN, Ng_M, Ks_M, mask_NM, M, N, Ks,
+        static_cast<__nv_bfloat16*>(G_logits_MN));
+    return LAUNCH_OK();
+}
+
+extern "C" __attribute__((visibility("default"))) int momoe_router_backward_compact(
+    const momoe_plan_t* plan, const float* gs_part, int32_t n_part, const int32_t* topk_idx_MK, const float* topk_w_MK,
+    const float* Ng_M, const float* Ks_M, int32_t Ks, void* G_logits_MN, momoe_stream_t stream) {
+    if (plan == nullptr || gs_part == nullptr || topk_idx_MK == nullptr || topk_w_MK == nullptr || Ng_M == nullptr ||
+        Ks_M == nullptr || G_logits_MN == nullptr || plan->pos_MK == nullptr)
+        return MOMOE_ERR_ARG;
+    if (n_part <= 0 || Ks < 0 || Ks >= plan->K || plan->M <= 0) return MOMOE_ERR_ARG;
+    if (plan->K > 32) return MOMOE_ERR_TOO_LARGE;
+    const int warps = 8;
+    router_backward_compact_kernel<<<cdiv(plan->M, warps), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        gs_part, n_part, plan->pos_MK, topk_idx_MK, topk_w_MK, Ng_M, Ks_M, plan->M, plan->N, plan->K, Ks,
         static_cast<__nv_bfloat16*>(G_logits_MN));
     return LAUNCH_OK();
 }

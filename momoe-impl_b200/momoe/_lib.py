@@ -52,6 +52,7 @@ _PROTOS = {
     "momoe_scatter_gs": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_router_backward": (C.c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp,
                                         c_vp]),
+    "momoe_router_backward_compact": (C.c_int, [c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp]),
     "momoe_bias_update": (C.c_int, [c_vp, c_vp, c_i32, c_i32, C.c_float, C.c_float, c_vp]),
     "momoe_ep_publish_counts": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_u32, c_vp, c_vp]),
     "momoe_ep_barrier": (C.c_int, [c_vp, c_i32, c_i32, c_u32, c_vp, c_vp]),

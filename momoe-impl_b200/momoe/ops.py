@@ -136,8 +136,9 @@ class RoutingPlan:
         return plan.build(topk_idx, topk_w)
 
 
-def route_topk(logits_MN, biases_N, K, Ks, dense=True):
-    """Router after the gate GEMM.  Returns (topk_idx, topk_w, dense dict or None)."""
+def route_topk(logits_MN, biases_N, K, Ks, dense=True, normalisers=False):
+    """Router after the gate GEMM.  Returns (topk_idx, topk_w, dict or None): the dict holds the dense outputs
+    (dense=True) or only Ng_M / Ks_M (normalisers=True)."""
     _lib.require_cuda(logits_MN, biases_N)
     M, N = logits_MN.shape
     dev = logits_MN.device
@@ -152,9 +153,12 @@ def route_topk(logits_MN, biases_N, K, Ks, dense=True):
                  s_postsoft_MN=torch.empty((M, N), dtype=torch.float32, device=dev),
                  Ng_M=torch.empty(M, dtype=torch.float32, device=dev),
                  Ks_M=torch.empty(M, dtype=torch.float32, device=dev))
+    elif normalisers:
+        d = dict(Ng_M=torch.empty(M, dtype=torch.float32, device=dev),
+                 Ks_M=torch.empty(M, dtype=torch.float32, device=dev))
     _call("momoe_route_topk", 1, lib.momoe_route_topk, ptr(logits_MN), ptr(biases_N), M, N, K, Ks, ptr(topk_idx), ptr(topk_w),
-                               ptr(d["mask_NM"]) if d else None, ptr(d["s_MN"]) if d else None,
-                               ptr(d["s_postsoft_MN"]) if d else None, ptr(d["Ng_M"]) if d else None,
+                               ptr(d["mask_NM"]) if dense else None, ptr(d["s_MN"]) if dense else None,
+                               ptr(d["s_postsoft_MN"]) if dense else None, ptr(d["Ng_M"]) if d else None,
                                ptr(d["Ks_M"]) if d else None, stream_ptr())
     return topk_idx, topk_w, d
 
@@ -235,6 +239,14 @@ def router_backward(G_s_NM, s_postsoft_MN, s_MN, Ng_M, Ks_M, mask_NM, Ks):
     out = torch.empty((M, N), dtype=torch.bfloat16, device=G_s_NM.device)
     _call("momoe_router_backward", 1, lib.momoe_router_backward, ptr(G_s_NM), G_s_NM.stride(0), G_s_NM.stride(1), ptr(s_postsoft_MN), ptr(s_MN),
                                     ptr(Ng_M), ptr(Ks_M), ptr(mask_NM), M, N, Ks, ptr(out), stream_ptr())
+    return out
+
+
+def router_backward_compact(plan, gs_part, Ng_M, Ks_M, Ks):
+    """Gradient of the gate logits (bf16 [M,N]) straight from the experts' per-row partial sums."""
+    out = torch.empty((plan.M, plan.N), dtype=torch.bfloat16, device=gs_part.device)
+    _call("momoe_router_backward_compact", 1, lib.momoe_router_backward_compact, plan.ref, ptr(gs_part),
+          gs_part.shape[1], ptr(plan.topk_idx), ptr(plan.topk_w), ptr(Ng_M), ptr(Ks_M), Ks, ptr(out), stream_ptr())
     return out
 
 

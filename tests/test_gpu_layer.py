@@ -91,8 +91,9 @@ LAYER_CASES = [
 ]
 
 
+@pytest.mark.parametrize("fused", [True, False], ids=["fused", "composed"])
 @pytest.mark.parametrize("B,S,D,H,N,K,Ks,sp,bias_std", LAYER_CASES)
-def test_moe_wrapper_against_oracle(momoe, B, S, D, H, N, K, Ks, sp, bias_std):
+def test_moe_wrapper_against_oracle(momoe, B, S, D, H, N, K, Ks, sp, bias_std, fused):
     gen = torch.Generator().manual_seed(B * S + D)
     x = torch.randn(B, S, D, generator=gen)
     W1 = (torch.randn(N, D, 2 * H, generator=gen) * 0.02).bfloat16()
@@ -102,6 +103,7 @@ def test_moe_wrapper_against_oracle(momoe, B, S, D, H, N, K, Ks, sp, bias_std):
     moe = momoe.MoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev), Wl1_ND2H=W1.to(dev),
                     Wl2_NHD=W2.to(dev))
     assert sorted(moe.state_dict()) == ["biases_N", "momoe.Wl1_ND2H", "momoe.Wl2_NHD", "router.Wg_DN"]
+    moe.fused = fused
     with torch.no_grad():
         moe.biases_N[:N - Ks] = (torch.randn(N - Ks, generator=gen) * bias_std).to(dev)
     biases0 = moe.biases_N.detach().cpu().clone()
@@ -128,6 +130,60 @@ def test_moe_wrapper_against_oracle(momoe, B, S, D, H, N, K, Ks, sp, bias_std):
     for e in np.nonzero(o["sizes"] == 0)[0]:
         assert float(moe.momoe.Wl1_ND2H.grad[e].float().abs().sum()) == 0.0
         assert float(moe.momoe.Wl2_NHD.grad[e].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("B,S,D,H,N,K,Ks,sp", [(2, 512, 512, 256, 16, 4, 1, 37), (1, 333, 192, 136, 12, 5, 2, 100),
+                                               (4, 1024, 1024, 512, 32, 4, 0, 0)])
+def test_fused_wrapper_equals_router_then_experts(momoe, B, S, D, H, N, K, Ks, sp):
+    """The single-node `MoE` path (compact routing end to end) against the literal TopKRouter -> MoMoE composition:
+    same output and expert gradients bit for bit; the gate gradient differs only by fp32 summation order."""
+    gen = torch.Generator().manual_seed(7 * S + N)
+    dev = "cuda"
+    x = torch.randn(B, S, D, generator=gen).to(dev)
+    W1 = (torch.randn(N, D, 2 * H, generator=gen) * 0.02).bfloat16().to(dev)
+    W2 = (torch.randn(N, H, D, generator=gen) * 0.02).bfloat16().to(dev)
+    Wg = (torch.randn(D, N, generator=gen) * 0.02).bfloat16().to(dev)
+    g = torch.randn(B, S, D, generator=gen).bfloat16().to(dev)
+    out = {}
+    for fused in (True, False):
+        moe = momoe.MoE(D, H, N, K, Ks, save_percent=sp, Wg_DN=Wg, Wl1_ND2H=W1, Wl2_NHD=W2)
+        moe.fused = fused
+        xg = x.clone().requires_grad_(True)
+        y = moe(xg)
+        y.backward(g)
+        _check_status()
+        out[fused] = (y.detach(), moe.momoe.Wl1_ND2H.grad, moe.momoe.Wl2_NHD.grad, xg.grad, moe.router.Wg_DN.grad,
+                      moe.biases_N.detach().clone())
+    a, b = out[True], out[False]
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert torch.equal(a[5], b[5])
+    assert cos(a[4].cpu(), b[4].cpu()) >= 0.99999 and max_rel(a[4].cpu(), b[4].cpu()) <= 1e-2
+    assert cos(a[3].cpu(), b[3].cpu()) >= 0.99999
+
+
+def test_forward_replays_as_a_cuda_graph(momoe):
+    """No host synchronisation and no host-side dependence on the routing: a captured forward pass, replayed on new
+    inputs of the same shape, gives what the eager call gives on them (bias update switched off so that both see the
+    same biases)."""
+    B, S, D, H, N, K, Ks = 1, 96, 256, 128, 16, 4, 1
+    dev = "cuda"
+    moe = momoe.MoE(D, H, N, K, Ks, save_percent=0, bias_update_rate=0.0)
+    gen = torch.Generator(device=dev).manual_seed(2)
+    x_static = torch.randn(B, S, D, generator=gen, device=dev).bfloat16()
+    with torch.no_grad():
+        moe(x_static)                                  # first call: every lazy initialisation happens here
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y_static = moe(x_static)
+        for seed in (3, 4):
+            x_new = torch.randn(B, S, D, generator=torch.Generator(device=dev).manual_seed(seed), device=dev).bfloat16()
+            x_static.copy_(x_new)
+            graph.replay()
+            torch.cuda.synchronize()
+            y_eager = moe(x_new)
+            assert torch.equal(y_static, y_eager)
+    _check_status()
 
 
 def test_forward_is_deterministic_and_training_reduces_loss(momoe):
