@@ -207,7 +207,7 @@ def run_triton_reference(args):
                                       save_percent=args.save_percent))), flush=True)
 
 
-INFER = dict(D=2048, H=768, N=128, K=8, tokens=(1, 8, 64, 256, 4096, 16384), w_std=0.02)
+INFER = dict(D=2048, H=768, N=128, K=8, tokens=(1, 8, 64, 256, 1024, 4096, 16384), w_std=0.02)
 
 
 def run_inference(args, dev):
@@ -227,16 +227,17 @@ def run_inference(args, dev):
     e_bias = 0.5 * torch.randn(N, generator=gen, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # larger than L2
     points = []
-    for T in c["tokens"]:
+    for T in ((args.infer_tokens,) if args.infer_tokens > 0 else c["tokens"]):
         x = torch.randn(1, T, D, generator=gen, device=dev).bfloat16()
         logits = (torch.randn(T, N, generator=gen, device=dev) + e_bias).bfloat16()
         zeros = torch.zeros(N, device=dev)
 
-        def fwd():
+        def fwd(inference=True):
             with torch.no_grad():
                 idx, w, _ = ops.route_topk(logits, zeros, K, 0, dense=False)
                 plan = ops.RoutingPlan.from_topk(idx, w, N, D, H, 0)
-                y, _, _ = ops.experts_forward(plan, x, layer.Wl1_ND2H.detach(), layer.Wl2_NHD.detach())
+                y, _, _ = ops.experts_forward(plan, x, layer.Wl1_ND2H.detach(), layer.Wl2_NHD.detach(),
+                                              inference=inference)
             return y, plan.sizes
 
         for _ in range(3):
@@ -247,6 +248,13 @@ def run_inference(args, dev):
         l0 = ops.LAUNCHES
         fwd()
         launches = ops.LAUNCHES - l0
+        if args.infer_tokens > 0:
+            for _ in range(3):
+                flush.zero_()
+                fwd()
+            torch.cuda.synchronize()
+            points.append(dict(tokens=T, experts_touched=touched, launches=launches))
+            continue
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             fwd()
@@ -267,10 +275,30 @@ def run_inference(args, dev):
         t_eager = timed(fwd)
         t_graph = timed(graph.replay)
         ops.check_status()
+        streaming = T * K <= ops.DECODE_MAX_AVG_ROWS * N
+        t_tile = None
+        if T * K <= 128 * N:
+            # the same batch forced through the other kernel family, for the cross-over
+            keep = ops.DECODE_MAX_AVG_ROWS
+            ops.DECODE_MAX_AVG_ROWS = 0 if streaming else 128
+            fwd()
+            graph2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph2):
+                fwd()
+            t_other = timed(graph2.replay)
+            del graph2
+            ops.DECODE_MAX_AVG_ROWS = keep
+            if not streaming:
+                t_tile, t_graph_streaming = t_graph, t_other
+            else:
+                t_tile, t_graph_streaming = t_other, t_graph
         nbytes = touched * 3 * D * H * 2 + T * D * 2 * 2 + T * K * (2 * D + 2 * H) * 2
         flops = 6.0 * T * K * D * H
-        points.append(dict(tokens=T, experts_touched=touched, launches=launches, ms_eager=round(t_eager, 4),
-                           ms_graph=round(t_graph, 4), hbm_gbs=round(nbytes / t_graph / 1e6, 1),
+        points.append(dict(tokens=T, experts_touched=touched, launches=launches,
+                           kernels="weight-streaming" if streaming else "256-row tiles",
+                           ms_eager=round(t_eager, 4), ms_graph=round(t_graph, 4),
+                           ms_graph_256_row_tiles=round(t_tile, 4) if t_tile is not None else None,
+                           ms_graph_weight_streaming=round(t_graph_streaming, 4) if t_tile is not None else None, hbm_gbs=round(nbytes / t_graph / 1e6, 1),
                            hbm_frac=round(nbytes / t_graph / 1e6 / peaks["hbm"], 3),
                            tflops=round(flops / t_graph / 1e9, 1),
                            tokens_per_s=round(T / t_graph * 1e3, 1)))
@@ -293,6 +321,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory leg (profiling runs)")
     ap.add_argument("--experts", type=int, default=CFG["N"], help="reduced case for profiler captures")
     ap.add_argument("--tokens", type=int, default=CFG["B"] * CFG["S"], help="reduced case for profiler captures")
+    ap.add_argument("--infer-tokens", type=int, default=0,
+                    help="inference workload: one batch size only, eager calls only (profiler captures)")
     ap.add_argument("--workload", default="headline", choices=["headline", "large_ep", "inference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

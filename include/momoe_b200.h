@@ -130,6 +130,17 @@ int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted, const void* 
 int momoe_down_scale(const momoe_plan_t* plan, const void* h_sorted, const void* W2_NHD, void* y_sorted,
                      momoe_stream_t stream);
 
+/* The two forward GEMMs for small token batches (inference: a few rows per expert, nothing kept for a backward
+ * pass).  Same inputs, outputs and arithmetic as momoe_up_swiglu with ab_mode 0 and momoe_down_scale; the weights
+ * are the 128-row side of the MMA and 32 tokens its N side, so that shared memory holds weights in flight instead of
+ * padding rows and the kernels run at the speed the weights cross HBM.  Only the 32-row blocks of a tile that hold
+ * real rows are written (blocks of padding rows keep whatever the buffer held).  Replace momoe/momoe.py:69-152 and
+ * :161-237 for forward-only calls. */
+int momoe_up_swiglu_decode(const momoe_plan_t* plan, const void* x_sorted, const void* W1_ND2H, void* h_sorted,
+                           momoe_stream_t stream);
+int momoe_down_scale_decode(const momoe_plan_t* plan, const void* h_sorted, const void* W2_NHD, void* y_sorted,
+                            momoe_stream_t stream);
+
 /* Backward of the down projection fused with the SwiGLU backward.  Replaces momoe/momoe.py:421-535 and the
  * G_s reduction of :684-703.  With Gh = g_sorted W2[e]^T (g_sorted is the UN-weighted gathered upstream
  * gradient) and a,b taken from the saved buffers (tile < sched[1]) or the recomputed ones:

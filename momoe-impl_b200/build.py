@@ -11,7 +11,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["common.cu", "routing.cu", "grouped_gemm.cu", "ep.cu"]
+SOURCES = ["common.cu", "routing.cu", "grouped_gemm.cu", "decode_gemm.cu", "ep.cu"]
 LIB_PATH = os.path.join(HERE, "momoe", "libmomoe_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -46,6 +46,8 @@ _PROTOS = {
     "momoe_combine_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_up_swiglu": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "momoe_down_scale": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
+    "momoe_up_swiglu_decode": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
+    "momoe_down_scale_decode": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_dgrad2_swiglu_bwd": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "momoe_dgrad1": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_wgrad": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp, c_vp]),

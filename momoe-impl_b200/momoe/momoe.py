@@ -36,7 +36,8 @@ class MoEFunction(torch.autograd.Function):
                 plan = ops.RoutingPlan.from_topk(compact[0], compact[1], N, D, H, save_percent)
             else:
                 plan = ops.RoutingPlan.from_mask(mask_NM.to(dev), s_NM.to(dev), K, D, H, save_percent)
-            y_MD, a_save, b_save = ops.experts_forward(plan, x_MD, W1, W2)
+            y_MD, a_save, b_save = ops.experts_forward(plan, x_MD, W1, W2,
+                                                          inference=not any(ctx.needs_input_grad))
         ctx.plan = plan
         ctx.shape = (B, S, D)
         ctx.in_devices = (x_BSD.device, s_NM.device)

@@ -175,14 +175,28 @@ def combine_rows(plan, src_sorted, cols):
     return dst
 
 
-def experts_forward(plan, x_MD, W1, W2):
+# Forward-only calls with at most this many rows per expert on average take the weight-streaming kernels
+# (momoe_up_swiglu_decode / momoe_down_scale_decode) instead of the 256-row tile kernels.
+DECODE_MAX_AVG_ROWS = int(os.environ.get("MOMOE_B200_DECODE_ROWS", "16"))
+
+
+def experts_forward(plan, x_MD, W1, W2, inference=False):
     """x_MD bf16 [M,D] contiguous; W1 bf16 [N,D,2H], W2 bf16 [N,H,D] contiguous.
-    Returns y_MD bf16 and the (a, b) buffers saved for the backward pass (None when nothing is saved)."""
+    Returns y_MD bf16 and the (a, b) buffers saved for the backward pass (None when nothing is saved).
+    inference=True: no backward pass will follow; small batches then use the weight-streaming kernels."""
     dev = x_MD.device
     D, H = plan.D, plan.H
     bf = dict(dtype=torch.bfloat16, device=dev)
     x_sorted = gather_rows(plan, x_MD, D)
     h = torch.empty((plan.rows_capacity, H), **bf)
+    if inference and plan.Msum <= DECODE_MAX_AVG_ROWS * plan.N:
+        _call("momoe_up_swiglu_decode", 1, lib.momoe_up_swiglu_decode, plan.ref, ptr(x_sorted), ptr(W1), ptr(h),
+              stream_ptr())
+        del x_sorted
+        y_sorted = torch.empty((plan.rows_capacity, D), **bf)
+        _call("momoe_down_scale_decode", 1, lib.momoe_down_scale_decode, plan.ref, ptr(h), ptr(W2), ptr(y_sorted),
+              stream_ptr())
+        return combine_rows(plan, y_sorted, D), None, None
     a_save = b_save = None
     mode = 0
     if plan.saved_tile_capacity > 0:

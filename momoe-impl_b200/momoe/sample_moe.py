@@ -36,7 +36,8 @@ class FusedMoEFunction(torch.autograd.Function):
             logits_MN = x_MD @ Wg
             topk_idx, topk_w, d = ops.route_topk(logits_MN, biases_N, K, Ks, dense=False, normalisers=True)
             plan = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, H, save_percent)
-            y_MD, a_save, b_save = ops.experts_forward(plan, x_MD, W1, W2)
+            y_MD, a_save, b_save = ops.experts_forward(plan, x_MD, W1, W2,
+                                                          inference=not any(ctx.needs_input_grad))
         ctx.plan = plan
         ctx.shape = (B, S, D)
         ctx.Ks = Ks

@@ -83,6 +83,63 @@ def test_up_swiglu_and_down_scale(ops, M, N, K, D, H, skew):
     assert float(ys[:rows][pad_rows].float().abs().sum()) == 0.0
 
 
+# decode shapes: few rows per expert, experts without rows, experts with more than one 32-row block and more than one
+# tile, widths that are not multiples of 128
+DECODE_SHAPES = SHAPES + [
+    (1, 128, 8, 2048, 768, 0.0),
+    (8, 128, 8, 2048, 768, 0.0),
+    (64, 32, 4, 1024, 520, 3.0),
+    (40, 4, 2, 136, 72, 0.0),
+]
+
+
+@pytest.mark.parametrize("M,N,K,D,H,skew", DECODE_SHAPES)
+def test_decode_kernels_match_fp32_and_tile_kernels(ops, M, N, K, D, H, skew):
+    """The weight-streaming forward kernels against fp32 torch on every real row, and against the 256-row tile kernels
+    (same arithmetic per element: equal up to the accumulation order inside the MMA)."""
+    _lib = lib_of(ops)
+    plan, x, W1, W2, pad = _setup(ops, M, N, K, D, H, skew)
+    xs = ops.gather_rows(plan, x, D)
+    rows = pad[-1]
+    nan = float("nan")
+    h = torch.full((plan.rows_capacity, H), nan, dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.lib.momoe_up_swiglu_decode(plan.ref, _lib.ptr(xs), _lib.ptr(W1), _lib.ptr(h), _lib.stream_ptr()),
+               "up decode")
+    ys = torch.full((plan.rows_capacity, D), nan, dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.lib.momoe_down_scale_decode(plan.ref, _lib.ptr(h), _lib.ptr(W2), _lib.ptr(ys), _lib.stream_ptr()),
+               "down decode")
+    h2 = torch.empty((plan.rows_capacity, H), dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.lib.momoe_up_swiglu(plan.ref, _lib.ptr(xs), _lib.ptr(W1), _lib.ptr(h2), None, None, 0,
+                                        _lib.stream_ptr()), "up")
+    ys2 = torch.empty((plan.rows_capacity, D), dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.lib.momoe_down_scale(plan.ref, _lib.ptr(h2), _lib.ptr(W2), _lib.ptr(ys2), _lib.stream_ptr()),
+               "down")
+    torch.cuda.synchronize()
+    ops.check_status()
+    real = plan.row_token[:rows] >= 0
+    assert real.sum() == M * K
+    h_ref = torch.zeros(rows, H, device="cuda")
+    y_ref = torch.zeros(rows, D, device="cuda")
+    for e in range(N):
+        lo, hi = pad[e], pad[e + 1]
+        if hi == lo:
+            continue
+        z = xs[lo:hi].float() @ W1[e].float()
+        a, b = z[:, :H], z[:, H:]
+        h_ref[lo:hi] = b * torch.sigmoid(b) * a
+        y_ref[lo:hi] = (torch.nan_to_num(h[lo:hi].float()) @ W2[e].float()) * plan.row_weight[lo:hi, None]
+    _close(h[:rows][real], h_ref[real], "h (decode)")
+    _close(ys[:rows][real], y_ref[real], "y_sorted (decode)")
+    _close(h[:rows][real], h2[:rows][real].float(), "h decode vs tile kernel")
+    _close(ys[:rows][real], ys2[:rows][real].float(), "y decode vs tile kernel")
+    # the layer output through the public forward sequence, both kernel families
+    y_dec, _, _ = ops.experts_forward(plan, x, W1, W2, inference=True)
+    y_std, _, _ = ops.experts_forward(plan, x, W1, W2, inference=False)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(y_dec, y_std.float(), "y decode vs tile kernel")
+
+
 @pytest.mark.parametrize("M,N,K,D,H,skew", SHAPES)
 @pytest.mark.parametrize("save_percent", [0, 50, 100])
 def test_backward_gemms(ops, M, N, K, D, H, skew, save_percent):
