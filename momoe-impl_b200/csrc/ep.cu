@@ -163,18 +163,35 @@ __device__ __forceinline__ void st_256(void* p, const uint4& a, const uint4& b) 
 // Gather + send.  One warp per row of this rank's (home) expert-major order.
 //   real row pr (token t, expert e, i-th of my tokens for e): src[t,:] -> owner(e)'s rows[dst_base[e] + i, :]
 // and, independently, the padding rows of MY OWN receive buffer are zeroed (nobody else writes them).
-__global__ void ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ home_row_token,
-                                        const int* __restrict__ home_tile_expert, const int* __restrict__ home_pad_off,
-                                        const int* __restrict__ home_sched, const float* __restrict__ home_row_weight,
-                                        const int* __restrict__ dst_base, int Nl, int vec_per_row, PeerPtrs rows,
-                                        PeerPtrs row_w, int* __restrict__ remote_row, int rank,
-                                        const int* __restrict__ local_count, const int* __restrict__ local_pad_off,
-                                        bool wide) {
+// Rows are visited round-robin over the destination ranks, starting with the next rank: consecutive warps (and the
+// successive rows of one warp) store to different GPUs, so every rank feeds all of its links at once and no GPU is
+// the target of all ranks at the same moment (marching through the expert-major order would make every rank send to
+// rank 0 first, then to rank 1, ...).
+__global__ void __launch_bounds__(256, 4)
+ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ home_row_token,
+                        const int* __restrict__ home_tile_expert, const int* __restrict__ home_pad_off,
+                        const float* __restrict__ home_row_weight, const int* __restrict__ dst_base, int Nl,
+                        int vec_per_row, PeerPtrs rows, PeerPtrs row_w, int* __restrict__ remote_row, int rank,
+                        int world, const int* __restrict__ local_count, const int* __restrict__ local_pad_off,
+                        bool wide) {
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
     const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int home_rows = home_sched[SCHED_PAD_ROWS];
-    for (int pr = wid; pr < home_rows; pr += warps_total) {
+    int max_len = 0;   // longest of the per-destination segments of my expert-major rows
+    for (int d = 0; d < world; ++d) max_len = max(max_len, home_pad_off[(d + 1) * Nl] - home_pad_off[d * Nl]);
+    const long long n_slots = static_cast<long long>(max_len) * world;
+    // a warp changes its destination from one row to the next (a bijection while the warp count is a multiple of the
+    // rank count), so that no warp only ever serves the fast local copies
+    const bool rotate = warps_total % world == 0;
+    for (long long j = wid; j < n_slots; j += warps_total) {
+        const int off = static_cast<int>(j / world);
+        int d = static_cast<int>(j - static_cast<long long>(off) * world);
+        if (rotate) d = static_cast<int>((d + j / warps_total) % world);
+        d += rank + 1;
+        if (d >= world) d -= world;
+        const int lo = home_pad_off[d * Nl];
+        if (off >= home_pad_off[(d + 1) * Nl] - lo) continue;
+        const int pr = lo + off;
         const int tok = home_row_token[pr];
         if (tok < 0) continue;
         const int e = home_tile_expert[pr / TILE_M];
@@ -184,7 +201,6 @@ __global__ void ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int
             continue;
         }
         const int row = base + (pr - home_pad_off[e]);
-        const int d = e / Nl;
         uint4* dst = static_cast<uint4*>(rows.p[d]) + static_cast<size_t>(row) * vec_per_row;
         const uint4* s = src + static_cast<size_t>(tok) * vec_per_row;
         if (wide) {
@@ -385,9 +401,8 @@ EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int
     for (int i = 0; i < world; ++i) align |= reinterpret_cast<uintptr_t>(r.p[i]);
     const bool wide = (cols % 16 == 0) && (align & 31) == 0;   // 256-bit stores need 32-byte aligned rows
     ep_dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), home->row_token, home->tile_expert, home->pad_off, home->sched,
-        home->row_weight, dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, local_count, local_pad_off,
-        wide);
+        static_cast<const uint4*>(src), home->row_token, home->tile_expert, home->pad_off, home->row_weight,
+        dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, world, local_count, local_pad_off, wide);
     return EP_LAUNCH_OK();
 }
 
