@@ -175,6 +175,8 @@ int momoe_router_backward(const float* G_s, int64_t gs_stride_n, int64_t gs_stri
 /* The same router backward without any dense [N,M] tensor: reads the per-row partial sums that
  * momoe_dgrad2_swiglu_bwd wrote (summed in the order momoe_scatter_gs uses), the compact routing of
  * momoe_route_topk and its two normalisers; unselected experts get a zero gradient.  Output G_logits_MN bf16 [M,N].
+ * plan->pos_MK may be NULL: gs_part is then already in the routing's compact order, row m*K+k for token m's k-th
+ * expert (with n_part = 1 this is dL/d topk_w).
  * Replaces momoe/momoe.py:721,699-703 (dense G_s) together with momoe/topk_router.py:11-56.  K <= 32. */
 int momoe_router_backward_compact(const momoe_plan_t* plan, const float* gs_part, int32_t n_part,
                                   const int32_t* topk_idx_MK, const float* topk_w_MK, const float* Ng_M,
@@ -236,6 +238,10 @@ int momoe_ep_reduce_gs(const float* gs_part, int32_t n_part, const int32_t* sche
 /* Dense G_s_NM fp32 [N,M] of this rank's tokens (zero where unselected), pulled from the owners' row_gs. */
 int momoe_ep_pull_gs(const momoe_plan_t* home, void* const* peer_row_gs, const int32_t* remote_row,
                      int32_t experts_per_rank, float* G_s_NM, int32_t world, momoe_stream_t stream);
+
+/* The same values in the compact order of the routing: gs_MK fp32 [M,K], entry (m,k) for token m's k-th expert. */
+int momoe_ep_pull_gs_compact(const momoe_plan_t* home, void* const* peer_row_gs, const int32_t* remote_row,
+                             int32_t experts_per_rank, float* gs_MK, int32_t world, momoe_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -325,6 +325,21 @@ __global__ void ep_pull_gs_kernel(PeerPtrs row_gs, const int* __restrict__ home_
     }
 }
 
+// The same values in the compact order of the routing: gs_MK[m, k] for the token's k-th expert.
+__global__ void ep_pull_gs_compact_kernel(PeerPtrs row_gs, const int* __restrict__ home_pos,
+                                          const int* __restrict__ home_tile_expert,
+                                          const int* __restrict__ remote_row, int Nl, int total,
+                                          float* __restrict__ gs_MK) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int pr = home_pos[i];
+        const int e = home_tile_expert[pr / TILE_M];
+        const float* src = static_cast<const float*>(row_gs.p[e / Nl]) + remote_row[pr];
+        float v;
+        asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(src));
+        gs_MK[i] = v;
+    }
+}
+
 static int fill_peers(PeerPtrs& out, void* const* ptrs, int world) {
     if (ptrs == nullptr) {
         for (int i = 0; i < EP_MAX_RANKS; ++i) out.p[i] = nullptr;
@@ -453,5 +468,18 @@ EP_API int momoe_ep_pull_gs(const momoe_plan_t* home, void* const* peer_row_gs, 
         return MOMOE_ERR_CUDA;
     ep_pull_gs_kernel<<<sm_count() * 4, 256, 0, st>>>(g, home->pos_MK, home->tile_expert, remote_row, experts_per_rank,
                                                       home->M, home->K, G_s_NM);
+    return EP_LAUNCH_OK();
+}
+
+EP_API int momoe_ep_pull_gs_compact(const momoe_plan_t* home, void* const* peer_row_gs, const int32_t* remote_row,
+                                    int32_t experts_per_rank, float* gs_MK, int32_t world, momoe_stream_t stream) {
+    if (home == nullptr || peer_row_gs == nullptr || remote_row == nullptr || gs_MK == nullptr ||
+        home->pos_MK == nullptr || home->tile_expert == nullptr)
+        return MOMOE_ERR_ARG;
+    if (world < 1 || world > EP_MAX_RANKS || experts_per_rank <= 0) return MOMOE_ERR_ARG;
+    PeerPtrs g;
+    if (fill_peers(g, peer_row_gs, world) != MOMOE_OK) return MOMOE_ERR_ARG;
+    ep_pull_gs_compact_kernel<<<sm_count() * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M * home->K, gs_MK);
     return EP_LAUNCH_OK();
 }

@@ -491,7 +491,8 @@ __global__ void router_backward_compact_kernel(const float* __restrict__ gs_part
     float g = 0.0f, w = 0.0f;
     int e = 0;
     if (lane < K) {
-        const size_t r = static_cast<size_t>(pos_MK[static_cast<size_t>(m) * K + lane]) * n_part;
+        const size_t i = static_cast<size_t>(m) * K + lane;
+        const size_t r = (pos_MK != nullptr ? static_cast<size_t>(pos_MK[i]) : i) * n_part;
         for (int p = 0; p < n_part; ++p) g += gs_part[r + p];
         w = topk_w[static_cast<size_t>(m) * K + lane];
         e = topk_idx[static_cast<size_t>(m) * K + lane];
@@ -695,7 +696,7 @@ extern "C" __attribute__((visibility("default"))) int momoe_router_backward_comp
     const momoe_plan_t* plan, const float* gs_part, int32_t n_part, const int32_t* topk_idx_MK, const float* topk_w_MK,
     const float* Ng_M, const float* Ks_M, int32_t Ks, void* G_logits_MN, momoe_stream_t stream) {
     if (plan == nullptr || gs_part == nullptr || topk_idx_MK == nullptr || topk_w_MK == nullptr || Ng_M == nullptr ||
-        Ks_M == nullptr || G_logits_MN == nullptr || plan->pos_MK == nullptr)
+        Ks_M == nullptr || G_logits_MN == nullptr)
         return MOMOE_ERR_ARG;
     if (n_part <= 0 || Ks < 0 || Ks >= plan->K || plan->M <= 0) return MOMOE_ERR_ARG;
     if (plan->K > 32) return MOMOE_ERR_TOO_LARGE;

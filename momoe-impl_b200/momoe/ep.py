@@ -22,7 +22,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import ops
-from .topk_router import TopKRouter
+from .topk_router import CompactRouterFunction, TopKRouter
 
 
 class DispatchMeta:
@@ -220,7 +220,7 @@ class PeerExpertParallelFunction(torch.autograd.Function):
     """Expert computation with dispatch / combine over peer memory (see the module docstring)."""
 
     @staticmethod
-    def forward(ctx, x_BSD, W1_local, W2_local, mask_NM, s_NM, topk_idx, topk_w, K, save_percent, bufs):
+    def forward(ctx, x_BSD, W1_local, W2_local, topk_idx, topk_w, K, save_percent, bufs):
         from . import _lib, ops
         lib, ptr, st = _lib.lib, _lib.ptr, _lib.stream_ptr
         B, S, D = x_BSD.shape
@@ -284,7 +284,7 @@ class PeerExpertParallelFunction(torch.autograd.Function):
         ctx.shape = (B, S, D)
         ctx.dims = (N, Nl, H, K)
         ctx.save_percent = save_percent
-        ctx.in_devices = (x_BSD.device, s_NM.device)
+        ctx.in_devices = (x_BSD.device, topk_w.device)
         ctx.has_ab = a_save is not None
         ctx.save_for_backward(*([W1, W2] + ([a_save, b_save] if ctx.has_ab else [])))
         ctx.mark_non_differentiable(sizes_global)
@@ -346,23 +346,23 @@ class PeerExpertParallelFunction(torch.autograd.Function):
                       ptr(bufs.row_gs), st())
             ev[2].record(main)
             G_x = torch.empty((M, D), **bf)
-            G_s = torch.empty((N, M), dtype=torch.float32, device=dev)
+            G_w = torch.empty((M, K), dtype=torch.float32, device=dev)
             with torch.cuda.stream(comm):
                 comm.wait_event(ev[2])
                 ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
                           ptr(status), st())
                 ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y,
                           ptr(remote_row), Nl, D, ptr(G_x), R, one_per_sm, st())
-                ops._call("momoe_ep_pull_gs", 1, lib.momoe_ep_pull_gs, home.ref, bufs.p_row_gs, ptr(remote_row), Nl,
-                          ptr(G_s), R, st())
+                ops._call("momoe_ep_pull_gs_compact", 1, lib.momoe_ep_pull_gs_compact, home.ref, bufs.p_row_gs,
+                          ptr(remote_row), Nl, ptr(G_w), R, st())
                 ev[3].record(comm)
             G_W2 = torch.empty_like(W2)
             ops._call("momoe_wgrad (W2)", 1, lib.momoe_wgrad, lp, ptr(hs), H, ptr(bufs.rows_g), D, ptr(G_W2), st())
             G_W1 = torch.empty_like(W1)
             ops._call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, lp, ptr(bufs.rows_x), D, ptr(gz), 2 * H, ptr(G_W1), st())
             main.wait_event(ev[3])
-        x_dev, s_dev = ctx.in_devices
-        return (G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_s.to(s_dev), None, None, None, None, None)
+        x_dev, w_dev = ctx.in_devices
+        return (G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_w.to(w_dev), None, None, None)
 
 
 class ExpertParallelMoE(nn.Module):
@@ -403,14 +403,17 @@ class ExpertParallelMoE(nn.Module):
             requires_grad=False)
 
     def forward(self, x_BSD):
-        x_BSD, mask_NM, s_NM = self.router(x_BSD, self.biases_N)
-        topk_idx, topk_w = mask_NM._momoe_topk
         B, S, _ = x_BSD.shape
         if self.transport == "peer":
+            # compact routing end to end: ids and weights [M,K]; the weights carry the gradient back to the router
+            topk_idx, topk_w = CompactRouterFunction.apply(x_BSD, self.router.Wg_DN, self.biases_N, self.N, self.K,
+                                                           self.Ks)
             bufs = self._peer_buffers(B * S)
-            y_BSD, sizes_N = PeerExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM,
-                                                              topk_idx, topk_w, self.K, self.save_percent, bufs)
+            y_BSD, sizes_N = PeerExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, topk_idx, topk_w,
+                                                              self.K, self.save_percent, bufs)
         else:
+            x_BSD, mask_NM, s_NM = self.router(x_BSD, self.biases_N)
+            topk_idx, topk_w = mask_NM._momoe_topk
             y_BSD, sizes_N = ExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM, topk_idx,
                                                           topk_w, self.K, self.save_percent, self.group)
         R = dist.get_world_size(self.group)

@@ -264,6 +264,18 @@ def router_backward_compact(plan, gs_part, Ng_M, Ks_M, Ks):
     return out
 
 
+def router_backward_from_topk_grad(G_w_MK, topk_idx, topk_w, Ng_M, Ks_M, N, Ks):
+    """Gradient of the gate logits (bf16 [M,N]) from dL/d topk_w (fp32 [M,K])."""
+    M, K = topk_idx.shape
+    G_w_MK = G_w_MK.to(torch.float32).contiguous()
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=topk_idx.device)
+    c = _lib.Plan(M=M, N=N, K=K, D=0, H=0, reserved=0, rows_capacity=0, sched=0, tile_expert=0, pad_off=0,
+                  row_token=0, row_weight=0, pos_MK=0, status=0, pair_info=0)
+    _call("momoe_router_backward_compact", 1, lib.momoe_router_backward_compact, C.byref(c), ptr(G_w_MK), 1,
+          ptr(topk_idx), ptr(topk_w), ptr(Ng_M), ptr(Ks_M), Ks, ptr(out), stream_ptr())
+    return out
+
+
 def bias_update_(biases_N, sizes_N, Ks, c_avg, rate):
     """In-place aux-loss-free bias update (one kernel instead of the reference's three torch ops)."""
     N = biases_N.shape[0]

@@ -39,6 +39,39 @@ class TopKRouterFunction(torch.autograd.Function):
         return G_x_MD.reshape(B, S, D).to(G_x_BSD.device), G_Wg, None, None, None, None
 
 
+class CompactRouterFunction(torch.autograd.Function):
+    """The same router with compact outputs only: expert ids int32 [M,K] (ascending, shared experts last) and their
+    weights fp32 [M,K]; the weights are the differentiable output.  No dense [N,M] tensor in either direction."""
+
+    @staticmethod
+    def forward(ctx, x_BSD, Wg_DN, biases_N, N, K, Ks):
+        B, S, D = x_BSD.shape
+        assert Wg_DN.dtype == torch.bfloat16, "Wg_DN must be of type torch.bfloat16"
+        require_cuda(Wg_DN)
+        dev = Wg_DN.device
+        x_MD = x_BSD.reshape(B * S, D).to(device=dev, dtype=torch.bfloat16)
+        Wg = Wg_DN.detach()
+        with torch.cuda.device(dev):
+            logits_MN = x_MD @ Wg
+            topk_idx, topk_w, d = ops.route_topk(logits_MN, biases_N, K, Ks, dense=False, normalisers=True)
+        ctx.save_for_backward(x_MD, Wg, topk_idx, topk_w, d["Ng_M"], d["Ks_M"])
+        ctx.dims = (B, S, D, N, Ks)
+        ctx.x_device = x_BSD.device
+        ctx.mark_non_differentiable(topk_idx)
+        return topk_idx, topk_w
+
+    @staticmethod
+    def backward(ctx, _i, G_w_MK):
+        x_MD, Wg, topk_idx, topk_w, Ng_M, Ks_M = ctx.saved_tensors
+        B, S, D, N, Ks = ctx.dims
+        dev = Wg.device
+        with torch.cuda.device(dev):
+            G_L = ops.router_backward_from_topk_grad(G_w_MK.to(dev), topk_idx, topk_w, Ng_M, Ks_M, N, Ks)
+            G_x_MD = G_L @ Wg.T
+            G_Wg = x_MD.T @ G_L
+        return G_x_MD.reshape(B, S, D).to(ctx.x_device), G_Wg, None, None, None, None
+
+
 class TopKRouter(nn.Module):
     def __init__(self, embedding_dim, num_experts, num_chosen_experts, num_shared_experts,
                  Wg_DN: torch.Tensor | None = None):
