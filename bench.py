@@ -321,6 +321,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory leg (profiling runs)")
     ap.add_argument("--experts", type=int, default=CFG["N"], help="reduced case for profiler captures")
     ap.add_argument("--tokens", type=int, default=CFG["B"] * CFG["S"], help="reduced case for profiler captures")
+    ap.add_argument("--forward-only", action="store_true",
+                    help="time forward passes only (per-call breakdown of the forward transfers; not the headline metric)")
     ap.add_argument("--infer-tokens", type=int, default=0,
                     help="inference workload: one batch size only, eager calls only (profiler captures)")
     ap.add_argument("--workload", default="headline", choices=["headline", "large_ep", "inference"])
@@ -390,6 +392,10 @@ def main():
         x_dev.grad = None
 
     def step_resident():
+        if args.forward_only:
+            with torch.no_grad():
+                moe(x_dev)
+            return
         zero_grads()
         y = moe(x_dev)
         y.backward(g_dev)
@@ -492,7 +498,7 @@ def main():
         return float(loss.item())   # device -> host read of the step's result
 
     ms_e2e = float("nan")
-    if not args.no_e2e:
+    if not args.no_e2e and not args.forward_only:
         prefetch(0)
         for i in range(3):
             step_e2e(i)
@@ -514,7 +520,13 @@ def main():
         cb = cpu_sample(2, 1)
         cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
-    if rank == 0:
+    if rank == 0 and args.forward_only:
+        # diagnostic output only: forward passes, per-call device times
+        print(json.dumps(dict(metric="MoE layer forward-only pass (diagnostic, not the headline metric)", unit="ms",
+                              n_gpus=world, steps=args.steps, ms_per_forward=ms, higher_is_better=False,
+                              config=dict(workload="forward only, %d tokens per GPU" % M, parallelism=parallelism),
+                              kernels=kernels)), flush=True)
+    elif rank == 0:
         line = dict(
             metric=METRIC if args.workload == "headline" else
             "MoE layer fwd+bwd tokens/sec (D%d H%d N%d K%d bf16)" % (D, H, N, K),
