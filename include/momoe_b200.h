@@ -235,11 +235,8 @@ int momoe_ep_combine_rows(const momoe_plan_t* home, void* const* peer_rows, cons
 int momoe_ep_reduce_gs(const float* gs_part, int32_t n_part, const int32_t* sched, float* row_gs,
                        momoe_stream_t stream);
 
-/* Dense G_s_NM fp32 [N,M] of this rank's tokens (zero where unselected), pulled from the owners' row_gs. */
-int momoe_ep_pull_gs(const momoe_plan_t* home, void* const* peer_row_gs, const int32_t* remote_row,
-                     int32_t experts_per_rank, float* G_s_NM, int32_t world, momoe_stream_t stream);
-
-/* The same values in the compact order of the routing: gs_MK fp32 [M,K], entry (m,k) for token m's k-th expert. */
+/* dL/d routing weight of this rank's (token, expert) pairs, pulled from the owners' row_gs:
+ * gs_MK fp32 [M,K], entry (m,k) for token m's k-th expert. */
 int momoe_ep_pull_gs_compact(const momoe_plan_t* home, void* const* peer_row_gs, const int32_t* remote_row,
                              int32_t experts_per_rank, float* gs_MK, int32_t world, momoe_stream_t stream);
 

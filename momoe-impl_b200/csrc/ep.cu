@@ -309,23 +309,8 @@ __global__ void ep_reduce_gs_kernel(const float* __restrict__ gs_part, int n_par
     }
 }
 
-// Dense G_s[e, m] (pre-zeroed) for this rank's tokens, pulled from the experts' owners.
-__global__ void ep_pull_gs_kernel(PeerPtrs row_gs, const int* __restrict__ home_pos,
-                                  const int* __restrict__ home_tile_expert, const int* __restrict__ remote_row, int Nl,
-                                  int M, int K, float* __restrict__ G_s_NM) {
-    const int total = M * K;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const int m = i / K;
-        const int pr = home_pos[i];
-        const int e = home_tile_expert[pr / TILE_M];
-        const float* src = static_cast<const float*>(row_gs.p[e / Nl]) + remote_row[pr];
-        float v;
-        asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(src));
-        G_s_NM[static_cast<size_t>(e) * M + m] = v;
-    }
-}
-
-// The same values in the compact order of the routing: gs_MK[m, k] for the token's k-th expert.
+// dL/d weight of this rank's (token, expert) pairs, pulled from the experts' owners: gs_MK[m, k] for token m's k-th
+// expert.
 __global__ void ep_pull_gs_compact_kernel(PeerPtrs row_gs, const int* __restrict__ home_pos,
                                           const int* __restrict__ home_tile_expert,
                                           const int* __restrict__ remote_row, int Nl, int total,
@@ -452,22 +437,6 @@ EP_API int momoe_ep_reduce_gs(const float* gs_part, int32_t n_part, const int32_
                               momoe_stream_t stream) {
     if (gs_part == nullptr || sched == nullptr || row_gs == nullptr || n_part <= 0) return MOMOE_ERR_ARG;
     ep_reduce_gs_kernel<<<sm_count() * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(gs_part, n_part, sched, row_gs);
-    return EP_LAUNCH_OK();
-}
-
-EP_API int momoe_ep_pull_gs(const momoe_plan_t* home, void* const* peer_row_gs, const int32_t* remote_row,
-                            int32_t experts_per_rank, float* G_s_NM, int32_t world, momoe_stream_t stream) {
-    if (home == nullptr || peer_row_gs == nullptr || remote_row == nullptr || G_s_NM == nullptr ||
-        home->pos_MK == nullptr || home->tile_expert == nullptr)
-        return MOMOE_ERR_ARG;
-    if (world < 1 || world > EP_MAX_RANKS || experts_per_rank <= 0) return MOMOE_ERR_ARG;
-    PeerPtrs g;
-    if (fill_peers(g, peer_row_gs, world) != MOMOE_OK) return MOMOE_ERR_ARG;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(G_s_NM, 0, sizeof(float) * static_cast<size_t>(home->N) * home->M, st) != cudaSuccess)
-        return MOMOE_ERR_CUDA;
-    ep_pull_gs_kernel<<<sm_count() * 4, 256, 0, st>>>(g, home->pos_MK, home->tile_expert, remote_row, experts_per_rank,
-                                                      home->M, home->K, G_s_NM);
     return EP_LAUNCH_OK();
 }
 

@@ -64,7 +64,6 @@ _PROTOS = {
                                          c_i32, c_vp]),
     "momoe_ep_combine_rows": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_i32, c_vp, c_i32, c_i32, c_vp]),
     "momoe_ep_reduce_gs": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_vp]),
-    "momoe_ep_pull_gs": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp]),
     "momoe_ep_pull_gs_compact": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp]),
 }
 for _name, (_res, _args) in _PROTOS.items():
