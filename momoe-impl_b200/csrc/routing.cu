@@ -335,54 +335,62 @@ __global__ void perm_fill_kernel(const int* __restrict__ topk_idx, const float* 
 }
 
 // ------------------------------------------------------------------------------------------ row movement
-// dst[r,:] = src[row_token[r],:], zeros on padding rows.  One warp per row.  Rows whose pitch is a multiple of
-// 32 bytes move in 256-bit pieces, four per lane in flight (a 4 KiB row is one batch of loads, then one of stores).
+// dst[r,:] = src[row_token[r],:], zeros on padding rows.  Rows whose pitch is a multiple of 32 bytes move in 256-bit
+// pieces, four per lane in flight (a 4 KiB row is one batch of loads, then K batches of stores).
 struct Vec256 {
     uint32_t v[8];
 };
 __device__ __forceinline__ Vec256 ld256_nc(const void* p) {
     Vec256 r;
-    // the source rows are read K times, far apart in time: ask L2 to keep them ...
-    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_last.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+    // every source row is read exactly once
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]),
                    "=r"(r.v[7])
                  : "l"(p));
     return r;
 }
 __device__ __forceinline__ void st256(void* p, const Vec256& r) {
-    // ... and to let the streamed copies go first
     asm volatile("st.global.L1::no_allocate.L2::evict_first.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p),
                  "r"(r.v[0]), "r"(r.v[1]), "r"(r.v[2]), "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]), "r"(r.v[7])
                  : "memory");
 }
-__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ row_token,
-                                   const int* __restrict__ sched, int vec_per_row, uint4* __restrict__ dst,
-                                   bool wide) {
+// Token-major: one warp reads a token's row ONCE and stores it to the K padded rows of the token's experts
+// (pos_MK), so the source crosses L2 once instead of K times; afterwards the padding rows are zeroed.
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ pos_MK,
+                                   const int* __restrict__ row_token, const int* __restrict__ sched, int M, int K,
+                                   int vec_per_row, uint4* __restrict__ dst, bool wide) {
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
-    const int rows = sched[SCHED_PAD_ROWS];
+    const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int n32 = vec_per_row >> 1;   // 32-byte pieces per row
-    for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps_total) {
-        const int tok = row_token[r];
-        uint4* d = dst + static_cast<size_t>(r) * vec_per_row;
-        if (tok >= 0) {
-            const uint4* s = src + static_cast<size_t>(tok) * vec_per_row;
-            if (wide) {
-                for (int c0 = lane; c0 < n32; c0 += 128) {
-                    Vec256 t[4];
+    for (int m = wid; m < M; m += warps_total) {
+        const uint4* s = src + static_cast<size_t>(m) * vec_per_row;
+        const int* pos = pos_MK + static_cast<size_t>(m) * K;
+        if (wide) {
+            for (int c0 = lane; c0 < n32; c0 += 128) {
+                Vec256 t[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (c0 + j * 32 < n32) t[j] = ld256_nc(s + 2 * (c0 + j * 32));
+                for (int j = 0; j < 4; ++j)
+                    if (c0 + j * 32 < n32) t[j] = ld256_nc(s + 2 * (c0 + j * 32));
+                for (int k = 0; k < K; ++k) {
+                    uint4* d = dst + static_cast<size_t>(__ldg(pos + k)) * vec_per_row;
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         if (c0 + j * 32 < n32) st256(d + 2 * (c0 + j * 32), t[j]);
                 }
-            } else {
-                for (int c = lane; c < vec_per_row; c += 32) d[c] = __ldg(s + c);
             }
         } else {
-            for (int c = lane; c < vec_per_row; c += 32) d[c] = make_uint4(0, 0, 0, 0);
+            for (int c = lane; c < vec_per_row; c += 32) {
+                const uint4 v = __ldg(s + c);
+                for (int k = 0; k < K; ++k) dst[static_cast<size_t>(__ldg(pos + k)) * vec_per_row + c] = v;
+            }
         }
+    }
+    const int rows = sched[SCHED_PAD_ROWS];
+    for (int r = wid; r < rows; r += warps_total) {
+        if (row_token[r] >= 0) continue;
+        uint4* d = dst + static_cast<size_t>(r) * vec_per_row;
+        for (int c = lane; c < vec_per_row; c += 32) d[c] = make_uint4(0, 0, 0, 0);
     }
 }
 
@@ -619,7 +627,7 @@ extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(co
 extern "C" __attribute__((visibility("default"))) int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
                                  momoe_stream_t stream) {
     if (plan == nullptr || src == nullptr || dst_sorted == nullptr || plan->row_token == nullptr ||
-        plan->sched == nullptr)
+        plan->sched == nullptr || plan->pos_MK == nullptr)
         return MOMOE_ERR_ARG;
     if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
     if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_sorted)) & 15) != 0) return MOMOE_ERR_ARG;
@@ -628,7 +636,8 @@ extern "C" __attribute__((visibility("default"))) int momoe_gather_rows(const mo
     const bool wide = (cols % 16 == 0) &&
                       (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_sorted)) & 31) == 0);
     gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), plan->row_token, plan->sched, cols / 8, static_cast<uint4*>(dst_sorted), wide);
+        static_cast<const uint4*>(src), plan->pos_MK, plan->row_token, plan->sched, plan->M, plan->K, cols / 8,
+        static_cast<uint4*>(dst_sorted), wide);
     return LAUNCH_OK();
 }
 
