@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this folder by running the UNMODIFIED reference kernels on CPU.
 
-Run in a container that has the reference checkout (default path below, or REFERENCE_ROOT):
+Run where a checkout of the reference is available, with REFERENCE_ROOT pointing at it:
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py
 
 The reference's Triton kernels execute under `TRITON_INTERPRET=1`.  Three shims touch Triton (not the
 reference): every autotuner is pinned to one of its own configurations (it cannot benchmark without a
@@ -18,7 +18,9 @@ import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
 sys.dont_write_bytecode = True
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(os.path.join(REF, "momoe")):
+    sys.exit("set REFERENCE_ROOT to a checkout of the reference repository (the folder that contains momoe/)")
 sys.path.insert(0, REF)
 
 import numpy as np  # noqa: E402
