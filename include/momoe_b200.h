@@ -74,6 +74,10 @@ int momoe_topk_from_mask(const int32_t* mask_NM, int64_t mask_stride_n, int64_t 
                          int64_t s_stride_n, int64_t s_stride_m, int32_t M, int32_t N, int32_t K,
                          int32_t* topk_idx_MK, float* topk_w_MK, int32_t* status, momoe_stream_t stream);
 
+/* Kernels momoe_build_permutation launches for this problem: 1 (up to 1024 tokens and 256 experts: the three passes
+ * and the initialisation of the padding rows run in one thread block) or 3 (+ two memsets).  Host arithmetic only. */
+int momoe_permutation_launches(int32_t M, int32_t N, int32_t K);
+
 /* Expert-major permutation from the compact routing.  Replaces momoe/momoe.py:821-842 (find_used_experts).
  * Outputs identical to the reference: sizes_N int64 [N], cumsums_N1 int32 [N+1], idx_Msum int32 [M*K],
  * which_Msum int32 [M*K] (slot = rank of the expert among the token's experts).  Plus the padded tables of

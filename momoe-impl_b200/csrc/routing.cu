@@ -182,15 +182,10 @@ __global__ void topk_from_mask_kernel(const int* __restrict__ mask, long long m_
 
 // ------------------------------------------------------------------------------------------ permutation
 // Pass A: per-chunk histogram.  counts[e*n_chunks + c] = tokens of chunk c routed to expert e.
-__global__ void perm_count_kernel(const int* __restrict__ topk_idx, int M, int N, int K, int n_chunks,
-                                  int* __restrict__ counts, int* status) {
-    extern __shared__ int sh[];
-    const int warps = blockDim.x >> 5;
-    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int* hist = sh + w * N;
-    const int chunk = blockIdx.x * warps + w;
+// One warp per chunk; hist = N ints of shared memory owned by the warp.
+__device__ __forceinline__ void perm_count_chunk(const int* __restrict__ topk_idx, int M, int N, int K, int n_chunks,
+                                                 int* counts, int* status, int chunk, int* hist, int lane) {
     const int m0 = chunk * CHUNK_TOKENS;
-    if (m0 >= M) return;
     for (int e = lane; e < N; e += 32) hist[e] = 0;
     __syncwarp();
     for (int t = lane; t < CHUNK_TOKENS; t += 32) {
@@ -205,16 +200,28 @@ __global__ void perm_count_kernel(const int* __restrict__ topk_idx, int M, int N
     }
     __syncwarp();
     for (int e = lane; e < N; e += 32) counts[static_cast<size_t>(e) * n_chunks + chunk] = hist[e];
+    __syncwarp();
 }
 
-// Pass B (one block): per-expert exclusive scan over chunks (in place), then the expert-level tables.
-__global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, int N, int K, long long save_rows,
-                                 long long* __restrict__ sizes, int* __restrict__ cumsums, int* __restrict__ pad_off,
-                                 int* __restrict__ tile_expert, int* __restrict__ pair_info, int* __restrict__ sched,
-                                 int tile_capacity) {
+__global__ void perm_count_kernel(const int* __restrict__ topk_idx, int M, int N, int K, int n_chunks,
+                                  int* __restrict__ counts, int* status) {
+    extern __shared__ int sh[];
+    const int warps = blockDim.x >> 5;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunk = blockIdx.x * warps + w;
+    if (chunk * CHUNK_TOKENS >= M) return;
+    perm_count_chunk(topk_idx, M, N, K, n_chunks, counts, status, chunk, sh + w * N, lane);
+}
+
+// Pass B (one block of at least N threads): per-expert exclusive scan over chunks (in place), then the expert-level
+// tables.  s_cum / s_pad (N+1 ints of shared memory each) keep cumsums / pad_off for a caller that goes on in the
+// same block.
+__device__ __forceinline__ void perm_scan_block(int* counts, int n_chunks, int M, int N, int K, long long save_rows,
+                                                long long* __restrict__ sizes, int* __restrict__ cumsums,
+                                                int* __restrict__ pad_off, int* __restrict__ tile_expert,
+                                                int* __restrict__ pair_info, int* __restrict__ sched,
+                                                int tile_capacity, int* s_cum, int* s_pad) {
     __shared__ int s_cnt[MAX_EXPERTS];
-    __shared__ int s_cum[MAX_EXPERTS + 1];
-    __shared__ int s_pad[MAX_EXPERTS + 1];
     __shared__ int s_pair[MAX_EXPERTS + 1];   // first pair of each expert (a pair = two consecutive tiles of one expert)
     __shared__ int s_saved;
     const int e = threadIdx.x;
@@ -286,22 +293,25 @@ __global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, 
     }
 }
 
+__global__ void perm_scan_kernel(int* __restrict__ counts, int n_chunks, int M, int N, int K, long long save_rows,
+                                 long long* __restrict__ sizes, int* __restrict__ cumsums, int* __restrict__ pad_off,
+                                 int* __restrict__ tile_expert, int* __restrict__ pair_info, int* __restrict__ sched,
+                                 int tile_capacity) {
+    __shared__ int s_cum[MAX_EXPERTS + 1];
+    __shared__ int s_pad[MAX_EXPERTS + 1];
+    perm_scan_block(counts, n_chunks, M, N, K, save_rows, sizes, cumsums, pad_off, tile_expert, pair_info, sched,
+                    tile_capacity, s_cum, s_pad);
+}
+
 // Pass C: every (token, k) pair gets its row.  Inside an expert rows ascend with the token id: a warp walks its
 // chunk 32 tokens at a time and ranks the lanes that chose the same expert with a per-expert bit mask.
-__global__ void perm_fill_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
-                                 const int* __restrict__ chunk_off, const int* __restrict__ cumsums,
-                                 const int* __restrict__ pad_off, int M, int N, int K, int n_chunks,
-                                 int* __restrict__ idx,
-                                 int* __restrict__ which, int* __restrict__ row_token, float* __restrict__ row_weight,
-                                 int* __restrict__ pos) {
-    extern __shared__ int sh[];
-    const int warps = blockDim.x >> 5;
-    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned* bits = reinterpret_cast<unsigned*>(sh) + w * 2 * N;
-    int* running = sh + w * 2 * N + N;
-    const int chunk = blockIdx.x * warps + w;
+__device__ __forceinline__ void perm_fill_chunk(const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
+                                                const int* chunk_off, const int* cumsums, const int* pad_off, int M,
+                                                int N, int K, int n_chunks, int* __restrict__ idx,
+                                                int* __restrict__ which, int* __restrict__ row_token,
+                                                float* __restrict__ row_weight, int* __restrict__ pos, int chunk,
+                                                unsigned* bits, int* running, int lane) {
     const int m0 = chunk * CHUNK_TOKENS;
-    if (m0 >= M) return;
     for (int e = lane; e < N; e += 32) running[e] = chunk_off[static_cast<size_t>(e) * n_chunks + chunk];
     for (int g0 = 0; g0 < CHUNK_TOKENS; g0 += 32) {
         for (int e = lane; e < N; e += 32) bits[e] = 0u;
@@ -332,6 +342,57 @@ __global__ void perm_fill_kernel(const int* __restrict__ topk_idx, const float* 
         for (int e = lane; e < N; e += 32) running[e] += __popc(bits[e]);
         __syncwarp();
     }
+}
+
+__global__ void perm_fill_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
+                                 const int* __restrict__ chunk_off, const int* __restrict__ cumsums,
+                                 const int* __restrict__ pad_off, int M, int N, int K, int n_chunks,
+                                 int* __restrict__ idx,
+                                 int* __restrict__ which, int* __restrict__ row_token, float* __restrict__ row_weight,
+                                 int* __restrict__ pos) {
+    extern __shared__ int sh[];
+    const int warps = blockDim.x >> 5;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunk = blockIdx.x * warps + w;
+    if (chunk * CHUNK_TOKENS >= M) return;
+    perm_fill_chunk(topk_idx, topk_w, chunk_off, cumsums, pad_off, M, N, K, n_chunks, idx, which, row_token,
+                    row_weight, pos, chunk, reinterpret_cast<unsigned*>(sh) + w * 2 * N, sh + w * 2 * N + N, lane);
+}
+
+// Small batches (a few chunks): the three passes and the initialisation of the padding rows in ONE thread block, so
+// that a forward pass of a handful of tokens is not a chain of five dependent launches.  Dynamic shared memory:
+// counts [N * n_chunks] followed by 2N ints of scratch for each of the SMALL_WARPS warps that walk chunks.
+constexpr int SMALL_WARPS = 16;
+constexpr int SMALL_MAX_TOKENS = SMALL_WARPS * CHUNK_TOKENS;   // one chunk per warp
+constexpr int SMALL_MAX_EXPERTS = 256;
+__global__ void __launch_bounds__(MAX_EXPERTS)
+perm_small_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int M, int N, int K,
+                  int n_chunks, long long save_rows, long long* __restrict__ sizes, int* __restrict__ cumsums,
+                  int* __restrict__ idx, int* __restrict__ which, int* __restrict__ pad_off,
+                  int* __restrict__ tile_expert, int* __restrict__ pair_info, int* __restrict__ sched,
+                  int* __restrict__ row_token, float* __restrict__ row_weight, int* __restrict__ pos,
+                  int rows_capacity, int tile_capacity, int* status) {
+    extern __shared__ int sh[];
+    __shared__ int s_cum[MAX_EXPERTS + 1];
+    __shared__ int s_pad[MAX_EXPERTS + 1];
+    int* counts = sh;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* scratch = sh + N * n_chunks + (w < SMALL_WARPS ? w : 0) * 2 * N;
+    for (int r = threadIdx.x; r < rows_capacity; r += blockDim.x) {   // padding rows: token -1, weight 0
+        row_token[r] = -1;
+        row_weight[r] = 0.0f;
+    }
+    if (w < SMALL_WARPS)
+        for (int chunk = w; chunk < n_chunks; chunk += SMALL_WARPS)
+            perm_count_chunk(topk_idx, M, N, K, n_chunks, counts, status, chunk, scratch, lane);
+    __syncthreads();
+    perm_scan_block(counts, n_chunks, M, N, K, save_rows, sizes, cumsums, pad_off, tile_expert, pair_info, sched,
+                    tile_capacity, s_cum, s_pad);
+    __syncthreads();   // also orders the initialisation of row_token / row_weight before the real rows are written
+    if (w < SMALL_WARPS)
+        for (int chunk = w; chunk < n_chunks; chunk += SMALL_WARPS)
+            perm_fill_chunk(topk_idx, topk_w, counts, s_cum, s_pad, M, N, K, n_chunks, idx, which, row_token,
+                            row_weight, pos, chunk, reinterpret_cast<unsigned*>(scratch), scratch + N, lane);
 }
 
 // ------------------------------------------------------------------------------------------ row movement
@@ -588,6 +649,11 @@ extern "C" __attribute__((visibility("default"))) size_t momoe_permutation_works
     return chunks * N * sizeof(int32_t);
 }
 
+extern "C" __attribute__((visibility("default"))) int momoe_permutation_launches(int32_t M, int32_t N, int32_t K) {
+    (void)K;
+    return (M <= SMALL_MAX_TOKENS && N <= SMALL_MAX_EXPERTS) ? 1 : 3;
+}
+
 extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(const int32_t* topk_idx_MK, const float* topk_w_MK, int32_t M, int32_t N,
                                        int32_t K, int64_t save_rows, int64_t* sizes_N, int32_t* cumsums_N1,
                                        int32_t* idx_Msum, int32_t* which_Msum, int32_t* pad_off, int32_t* tile_expert,
@@ -607,6 +673,18 @@ extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(co
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int* counts = static_cast<int*>(workspace);
     const int n_chunks = cdiv(M, CHUNK_TOKENS);
+    if (momoe_permutation_launches(M, N, K) == 1) {
+        // one launch: a handful of tokens must not wait for five dependent launches
+        const size_t smem = sizeof(int) * (static_cast<size_t>(N) * n_chunks + static_cast<size_t>(SMALL_WARPS) * 2 * N);
+        if (cudaFuncSetAttribute(perm_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess)
+            return MOMOE_ERR_CUDA;
+        perm_small_kernel<<<1, MAX_EXPERTS, smem, st>>>(
+            topk_idx_MK, topk_w_MK, M, N, K, n_chunks, save_rows, reinterpret_cast<long long*>(sizes_N), cumsums_N1,
+            idx_Msum, which_Msum, pad_off, tile_expert, pair_info, sched, row_token, row_weight, pos_MK,
+            static_cast<int>(rows_capacity), static_cast<int>(momoe_tile_capacity(M, K, N)), status);
+        return LAUNCH_OK();
+    }
     const int warps = 4;
     const int blocks = cdiv(n_chunks, warps);
     // padding rows: token -1, weight 0

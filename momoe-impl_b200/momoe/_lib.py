@@ -37,6 +37,7 @@ _PROTOS = {
                                    c_vp]),
     "momoe_topk_from_mask": (C.c_int, [c_vp, c_i64, c_i64, c_vp, c_i64, c_i64, c_i32, c_i32, c_i32, c_vp, c_vp, c_vp,
                                        c_vp]),
+    "momoe_permutation_launches": (C.c_int, [c_i32, c_i32, c_i32]),
     "momoe_permutation_workspace_bytes": (c_sz, [c_i32, c_i32, c_i32]),
     "momoe_build_permutation": (C.c_int, [c_vp, c_vp, c_i32, c_i32, c_i32, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                                           c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_sz, c_vp, c_vp]),

@@ -106,7 +106,8 @@ class RoutingPlan:
         self.topk_idx, self.topk_w = topk_idx, topk_w
         nbytes = int(lib.momoe_permutation_workspace_bytes(self.M, self.N, self.K))
         ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=self.device)
-        _call("momoe_build_permutation", 3, lib.momoe_build_permutation, ptr(topk_idx), ptr(topk_w), self.M, self.N, self.K, self.save_rows,
+        _call("momoe_build_permutation", int(lib.momoe_permutation_launches(self.M, self.N, self.K)),
+              lib.momoe_build_permutation, ptr(topk_idx), ptr(topk_w), self.M, self.N, self.K, self.save_rows,
                                           ptr(self.sizes), ptr(self.cumsums), ptr(self.idx), ptr(self.which),
                                           ptr(self.pad_off), ptr(self.tile_expert), ptr(self.pair_info), ptr(self.sched),
                                           ptr(self.row_token), ptr(self.row_weight), ptr(self.pos),
