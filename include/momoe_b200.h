@@ -111,7 +111,8 @@ int momoe_build_permutation_static(const int32_t* topk_idx_MK, const float* topk
                                    int32_t* pos_MK, int64_t rows_capacity, int32_t* status, momoe_stream_t stream);
 
 /* dst[r,:] = src[row_token[r],:] (zeros on padding rows), bf16, `cols` columns (multiple of 8).  Each source row is
- * read once and stored to the token's K rows (plan->pos_MK).
+ * read once and stored to the token's K rows (plan->pos_MK); with plan->pos_MK == NULL the rows are fetched one by
+ * one from plan->row_token alone.
  * Replaces the row gathers of momoe/momoe.py:116-118 and :298-350. */
 int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
                       momoe_stream_t stream);

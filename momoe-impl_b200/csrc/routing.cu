@@ -455,6 +455,24 @@ __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __r
     }
 }
 
+// Row-major form for callers that only have the row table (plan->pos_MK == NULL): one warp per destination row.
+__global__ void gather_rows_by_row_kernel(const uint4* __restrict__ src, const int* __restrict__ row_token,
+                                          const int* __restrict__ sched, int vec_per_row, uint4* __restrict__ dst) {
+    const int lane = threadIdx.x & 31;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    const int rows = sched[SCHED_PAD_ROWS];
+    for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps_total) {
+        const int tok = row_token[r];
+        uint4* d = dst + static_cast<size_t>(r) * vec_per_row;
+        if (tok >= 0) {
+            const uint4* s = src + static_cast<size_t>(tok) * vec_per_row;
+            for (int c = lane; c < vec_per_row; c += 32) d[c] = __ldg(s + c);
+        } else {
+            for (int c = lane; c < vec_per_row; c += 32) d[c] = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
 __device__ __forceinline__ void acc_bf16x8(const uint4& q, float (&a)[8]) {
     a[0] += __uint_as_float(q.x << 16); a[1] += __uint_as_float(q.x & 0xFFFF0000u);
     a[2] += __uint_as_float(q.y << 16); a[3] += __uint_as_float(q.y & 0xFFFF0000u);
@@ -705,7 +723,7 @@ extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(co
 extern "C" __attribute__((visibility("default"))) int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
                                  momoe_stream_t stream) {
     if (plan == nullptr || src == nullptr || dst_sorted == nullptr || plan->row_token == nullptr ||
-        plan->sched == nullptr || plan->pos_MK == nullptr)
+        plan->sched == nullptr)
         return MOMOE_ERR_ARG;
     if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
     if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_sorted)) & 15) != 0) return MOMOE_ERR_ARG;
@@ -713,9 +731,13 @@ extern "C" __attribute__((visibility("default"))) int momoe_gather_rows(const mo
     // 256-bit moves need every row to start on a 32-byte boundary
     const bool wide = (cols % 16 == 0) &&
                       (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_sorted)) & 31) == 0);
-    gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4*>(src), plan->pos_MK, plan->row_token, plan->sched, plan->M, plan->K, cols / 8,
-        static_cast<uint4*>(dst_sorted), wide);
+    if (plan->pos_MK == nullptr)
+        gather_rows_by_row_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint4*>(src), plan->row_token, plan->sched, cols / 8, static_cast<uint4*>(dst_sorted));
+    else
+        gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint4*>(src), plan->pos_MK, plan->row_token, plan->sched, plan->M, plan->K, cols / 8,
+            static_cast<uint4*>(dst_sorted), wide);
     return LAUNCH_OK();
 }
 
