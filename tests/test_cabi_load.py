@@ -39,6 +39,11 @@ def test_capacity_arithmetic(lib):
     assert lib.lib.momoe_sorted_rows_capacity(16384, 8, 128) == (1024 + 128) * 128
     assert lib.lib.momoe_sorted_rows_capacity(1, 8, 128) == (1 + 128) * 128
     assert lib.lib.momoe_permutation_workspace_bytes(16384, 128, 8) == (16384 // 64) * 128 * 4
+    # small batches are permuted by one thread block, large ones by three kernels
+    assert lib.lib.momoe_permutation_launches(64, 128, 8) == 1
+    assert lib.lib.momoe_permutation_launches(1024, 256, 8) == 1
+    assert lib.lib.momoe_permutation_launches(1025, 128, 8) == 3
+    assert lib.lib.momoe_permutation_launches(64, 257, 8) == 3
 
 
 def test_bad_arguments_rejected_on_host(lib):
