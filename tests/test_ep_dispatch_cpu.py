@@ -138,3 +138,48 @@ def test_missing_rank_ends_counts_exchange_with_an_error():
         if p.is_alive():
             p.kill()
     assert codes == [0, 0], codes
+
+
+def _dispatch_visit_order(seg_len, rank, warps_total):
+    """Host restatement of the row schedule of ep_dispatch_rows_kernel (csrc/ep.cu): slot j of the grid-stride loop
+    -> (destination rank, offset inside that destination's segment of the expert-major rows), or None."""
+    world = len(seg_len)
+    max_len = max(seg_len)
+    rotate = warps_total % world == 0
+    visits = []
+    for wid in range(warps_total):
+        j = wid
+        while j < max_len * world:
+            off = j // world
+            d = j - off * world
+            if rotate:
+                d = (d + j // warps_total) % world
+            d += rank + 1
+            if d >= world:
+                d -= world
+            if off < seg_len[d]:
+                visits.append((wid, j // warps_total, d, off))
+            j += warps_total
+    return visits
+
+
+@pytest.mark.parametrize("world,warps_total", [(1, 8), (2, 8), (2, 1184), (4, 1184), (8, 9472), (8, 1184), (3, 8), (6, 40)])
+def test_dispatch_schedule_visits_every_row_once_and_spreads_destinations(world, warps_total):
+    rng = np.random.default_rng(world * 1000 + warps_total)
+    seg_len = [int(v) * 128 for v in rng.integers(0, 40, size=world)]
+    seg_len[rng.integers(0, world)] = 40 * 128          # at least one long segment
+    for rank in range(world):
+        visits = _dispatch_visit_order(seg_len, rank, warps_total)
+        seen = sorted((d, off) for _, _, d, off in visits)
+        want = sorted((d, off) for d in range(world) for off in range(seg_len[d]))
+        assert seen == want                              # a bijection onto the rows, whatever the warp count
+        if world > 1 and warps_total % world == 0:
+            # in one pass of the grid the warps address every destination equally often, the next rank first ...
+            first = [d for wid, it, d, off in visits if it == 0]
+            if min(seg_len) > warps_total // world:
+                counts = np.bincount(first, minlength=world)
+                assert counts.min() == counts.max()
+            # ... and a warp changes destination from one of its rows to the next
+            w0 = [d for wid, it, d, off in visits if wid == 0][:world]
+            if min(seg_len) > (world * warps_total) // world:
+                assert len(set(w0)) == world
