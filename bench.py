@@ -348,6 +348,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # the only NCCL collectives here are barriers and the reduction of a timing scalar: no in-switch reduction
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
         dist.barrier()
     import momoe
