@@ -133,3 +133,9 @@ if __name__ == "__main__":
     # everything saved
     run_case("sp100_d128_h64_n4_k2", 2, 48, 128, 64, 4, 2, 0, 100, tile_cfg=0, block_rows=128,
              bias_std=0.02, seed=3)
+    # 24 tokens, 16 experts, strong bias: all tokens land on two experts, fourteen experts receive nothing
+    run_case("empty_experts_d128_h64_n16_k2", 1, 24, 128, 64, 16, 2, 0, 0, tile_cfg=0, block_rows=128,
+             bias_std=0.5, seed=4)
+    # two shared experts, K = 5, H not a multiple of 64, save_percent 30
+    run_case("shared2_d128_h96_n12_k5_ks2_sp30", 1, 80, 128, 96, 12, 5, 2, 30, tile_cfg=0, block_rows=128,
+             bias_std=0.05, seed=5)
