@@ -139,3 +139,9 @@ if __name__ == "__main__":
     # two shared experts, K = 5, H not a multiple of 64, save_percent 30
     run_case("shared2_d128_h96_n12_k5_ks2_sp30", 1, 80, 128, 96, 12, 5, 2, 30, tile_cfg=0, block_rows=128,
              bias_std=0.05, seed=5)
+    # top-8 of 32 experts on 64 tokens: a realistic K with several experts without tokens
+    run_case("top8_d128_h64_n32_k8", 1, 64, 128, 64, 32, 8, 0, 0, tile_cfg=0, block_rows=128,
+             bias_std=0.02, seed=6)
+    # save_percent 99 with 64-row tiles: only the last rows of the last expert are recomputed
+    run_case("sp99_d64_h64_n4_k2_tiles64", 1, 300, 64, 64, 4, 2, 0, 99, tile_cfg=2, block_rows=64,
+             bias_std=0.0, seed=7)
