@@ -207,6 +207,119 @@ def run_triton_reference(args):
                                       save_percent=args.save_percent))), flush=True)
 
 
+def ep_parity_preflight(rank, world, dev):
+    """Untimed correctness check of the expert-parallel path before a multi-GPU measurement: one reduced step (1024
+    tokens per rank, D512 H256, 8 experts per rank, K=4, save_percent 50) through `ExpertParallelMoE` on this rank's
+    token shard and expert block against the single-GPU `MoE` on all tokens and all experts, same seeded problem on
+    every rank.  y must be identical bit for bit (same kernels, same per-row arithmetic, same summation order);
+    gradients are compared by cosine similarity.  Every figure is the worst over the ranks."""
+    import torch.distributed as dist
+    import momoe
+    from momoe import ep, ops
+    Mr, D, H, K, Ks, sp = 1024, 512, 256, 4, 0, 50
+    N = 8 * world
+    Nl = N // world
+    g = torch.Generator().manual_seed(4321)
+    x_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
+    W1 = (torch.randn(N, D, 2 * H, generator=g) * 0.03).bfloat16()
+    W2 = (torch.randn(N, H, D, generator=g) * 0.03).bfloat16()
+    Wg = (torch.randn(D, N, generator=g) * 0.05).bfloat16()
+    gy_all = torch.randn(world, 1, Mr, D, generator=g).bfloat16()
+    biases = torch.randn(N, generator=g) * 0.05
+
+    def cos(a, b):
+        a, b = a.double().flatten(), b.double().flatten()
+        return float(a @ b / (a.norm() * b.norm()).clamp_min(1e-300))
+
+    ref = momoe.MoE(D, H, N, K, Ks, save_percent=sp, Wg_DN=Wg.to(dev), Wl1_ND2H=W1.to(dev), Wl2_NHD=W2.to(dev))
+    moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, Wg_DN=Wg.to(dev),
+                               Wl1_ND2H=W1[rank * Nl:(rank + 1) * Nl].to(dev),
+                               Wl2_NHD=W2[rank * Nl:(rank + 1) * Nl].to(dev), capacity_factor=float(world))
+    with torch.no_grad():
+        ref.biases_N.copy_(biases.to(dev))
+        moe.biases_N.copy_(biases.to(dev))
+    xa = x_all.reshape(1, world * Mr, D).to(dev).requires_grad_(True)
+    ya = ref(xa)
+    ya.backward(gy_all.reshape(1, world * Mr, D).to(dev))
+    xr = x_all[rank].to(dev).requires_grad_(True)
+    yr = moe(xr)
+    yr.backward(gy_all[rank].to(dev))
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    sl = slice(rank * Mr, (rank + 1) * Mr)
+    gwg = moe.router.Wg_DN.grad.float().clone()
+    dist.all_reduce(gwg)
+    res = torch.tensor([1.0 if torch.equal(yr[0], ya[0, sl]) else 0.0,
+                        cos(xr.grad[0], xa.grad[0, sl]),
+                        cos(moe.Wl1_ND2H.grad, ref.momoe.Wl1_ND2H.grad[rank * Nl:(rank + 1) * Nl]),
+                        cos(moe.Wl2_NHD.grad, ref.momoe.Wl2_NHD.grad[rank * Nl:(rank + 1) * Nl]),
+                        cos(gwg, ref.router.Wg_DN.grad),
+                        1.0 if torch.equal(moe.biases_N, ref.biases_N) else 0.0], dtype=torch.float64, device=dev)
+    dist.all_reduce(res, op=dist.ReduceOp.MIN)
+    r = res.tolist()
+    del ref, moe, ya, yr
+    torch.cuda.empty_cache()
+    return dict(case="1024 tokens per rank, D512 H256, 8 experts per rank, K4, save_percent 50, peer transport",
+                y_bit_exact=bool(r[0] == 1.0), dx_cos=round(r[1], 6), dw1_cos=round(r[2], 6), dw2_cos=round(r[3], 6),
+                dwg_cos=round(r[4], 6), bias_update_equal=bool(r[5] == 1.0))
+
+
+def extra_records(args, dev, moe, x_dev, g_dev, M):
+    """Untimed-for-`value` records of the 1-GPU line: the same layer at save_percent 100 (nothing recomputed), and the
+    unmodified reference package's own Triton kernels on this GPU (a subprocess of `--impl reference-triton`)."""
+    import momoe
+    out = {}
+    try:
+        m100 = momoe.MoE(moe.D, moe.H, moe.N, moe.K, moe.Ks, save_percent=100, Wg_DN=moe.router.Wg_DN.detach(),
+                         Wl1_ND2H=moe.momoe.Wl1_ND2H.detach(), Wl2_NHD=moe.momoe.Wl2_NHD.detach())
+
+        def step():
+            for p in m100.parameters():
+                p.grad = None
+            x_dev.grad = None
+            m100(x_dev).backward(g_dev)
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms100 = e0.elapsed_time(e1) / args.steps
+        out["save_percent_100"] = dict(ms_per_step=round(ms100, 4), tokens_per_s=round(M / (ms100 * 1e-3), 1),
+                                       steps=args.steps)
+        del m100
+        for p in moe.parameters():
+            p.grad = None
+        x_dev.grad = None
+        torch.cuda.empty_cache()
+    except Exception as err:   # a record, not the measurement: never take the line down
+        out["save_percent_100"] = {"unavailable": repr(err)[:200]}
+    ref_dir = os.path.join(ROOT, "baseline", "_ref", "momoe")
+    if not os.path.isdir(ref_dir):
+        out["reference_triton"] = {"unavailable": "baseline/_ref is not installed"}
+        return out
+    try:
+        res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-triton", "--steps",
+                              str(args.steps), "--warmup", "12", "--save-percent", str(args.save_percent)],
+                             capture_output=True, text=True, timeout=600, cwd=ROOT)
+        lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
+        d = json.loads(lines[-1]) if lines else {"unavailable": (res.stderr or "no output")[-300:]}
+        if "ms_per_step" in d:
+            out["reference_triton"] = dict(ms_per_step=round(d["ms_per_step"], 4), tokens_per_s=round(d["value"], 1),
+                                           save_percent=args.save_percent, steps=d.get("steps"),
+                                           what="unmodified reference package (baseline/_ref), its Triton kernels "
+                                                "autotuned during 12 warm-up steps, same GPU, layer and protocol")
+        else:
+            out["reference_triton"] = {"unavailable": str(d.get("unavailable"))[:300]}
+    except Exception as err:
+        out["reference_triton"] = {"unavailable": repr(err)[:200]}
+    return out
+
+
 INFER = dict(D=2048, H=768, N=128, K=8, tokens=(1, 8, 64, 256, 1024, 4096, 16384), w_std=0.02)
 
 
@@ -319,6 +432,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-memory leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the untimed extra records of the 1-GPU line (save_percent 100, reference package)")
     ap.add_argument("--experts", type=int, default=CFG["N"], help="reduced case for profiler captures")
     ap.add_argument("--tokens", type=int, default=CFG["B"] * CFG["S"], help="reduced case for profiler captures")
     ap.add_argument("--forward-only", action="store_true",
@@ -359,6 +474,8 @@ def main():
         if rank == 0:
             run_inference(args, dev)
         return
+
+    ep_parity = ep_parity_preflight(rank, world, dev) if world > 1 else None
 
     c = dict(CFG if args.workload == "headline" else LARGE_EP)
     reduced = args.workload == "headline" and (args.experts != c["N"] or args.tokens != c["B"] * c["S"])
@@ -442,9 +559,9 @@ def main():
     # algorithmic flops of one launch, in units of Msum*D*H (up/gate 4, down 2, dgrad-2 2, wgrads 2 and 4, dgrad-1 4)
     flops = {"momoe_up_swiglu": 4, "momoe_up_swiglu (recompute)": 4, "momoe_down_scale": 2,
              "momoe_dgrad2_swiglu_bwd": 2, "momoe_wgrad (W2)": 2, "momoe_wgrad (W1)": 4, "momoe_dgrad1": 4}
-    # DRAM bytes per launch (read + write) from the ncu capture summarised in
-    # profiles/grouped_gemm_reduced_case_ncu_full.md (32 experts, 4096 tokens), per (expert x token) unit; traffic
-    # grows in proportion to both, so it is scaled to this run's experts and tokens.
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, MB) from an ncu capture of the reduced case
+    # (--experts 32 --tokens 4096); traffic grows in proportion to experts (weights) and tokens (activations), so it is
+    # scaled to this run's experts and tokens.
     ncu_mb_small = {"momoe_up_swiglu": 474, "momoe_up_swiglu (recompute)": 535, "momoe_down_scale": 316,
                     "momoe_dgrad2_swiglu_bwd": 611, "momoe_wgrad (W2)": 319, "momoe_wgrad (W1)": 519,
                     "momoe_dgrad1": 534}
@@ -517,9 +634,14 @@ def main():
     ms_e2e = float(t.item())
     ops.check_status(dev)
 
+    extras = {}
+    if rank == 0 and world == 1 and args.workload == "headline" and not reduced and not args.forward_only \
+            and not args.no_extras:
+        extras = extra_records(args, dev, moe, x_dev, g_dev, M)
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "headline":
-        cb = cpu_sample(2, 1)
+        cb = cpu_sample(6, 1)
         cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
     if rank == 0 and args.forward_only:
@@ -546,6 +668,9 @@ def main():
             gpu_launches=launches, clocks=clocks, roofline=roofline, cpu_baseline=cpu_baseline,
             layer_tflops=round(layer_tflops, 1), layer_frac_of_peak=round(layer_tflops / peaks["tflops"], 4),
             kernels=kernels)
+        line.update(extras)
+        if ep_parity is not None:
+            line["ep_parity"] = ep_parity
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -131,6 +131,15 @@ int momoe_combine_rows(const momoe_plan_t* plan, const void* src_sorted, int32_t
 int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted, const void* W1_ND2H, void* h_sorted,
                     void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream);
 
+/* momoe_up_swiglu with the row gather folded into the GEMM's operand loads, as the reference's kernel does
+ * (momoe/momoe.py:116-118: `x` rows are fetched through the expert-major index inside lin1_kernel).  x_MD is the
+ * token-major input bf16 [plan->M, D]; row r of the A operand is x_MD[plan->row_token[r], :], fetched four rows per
+ * TMA row-gather load.  No expert-major copy of x exists.  A padding row (row_token -1) repeats the first row of its
+ * 128-row tile, so its h, a, b are those of a real row of the same expert, not zeros; everything downstream
+ * multiplies padding rows by their zero routing weight.  Other arguments as momoe_up_swiglu. */
+int momoe_up_swiglu_tokens(const momoe_plan_t* plan, const void* x_MD, const void* W1_ND2H, void* h_sorted,
+                           void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream);
+
 /* Down grouped GEMM with the routing weight in the epilogue: y_sorted[r,:] = bf16(w[r] * (h[r,:] W2[e])).
  * Replaces momoe/momoe.py:161-237. */
 int momoe_down_scale(const momoe_plan_t* plan, const void* h_sorted, const void* W2_NHD, void* y_sorted,
@@ -157,6 +166,14 @@ int momoe_dgrad2_swiglu_bwd(const momoe_plan_t* plan, const void* g_sorted, cons
                             const void* a_saved, const void* b_saved, const void* a_recomp, const void* b_recomp,
                             void* gz_sorted, void* hs_sorted, float* gs_part, momoe_stream_t stream);
 
+/* momoe_dgrad2_swiglu_bwd reading the upstream gradient token-major: g_MD bf16 [plan->M, D], rows fetched through
+ * plan->row_token inside the GEMM.  Replaces the pre-gather of momoe/momoe.py:298-350 (making_nice_scatter_kernel)
+ * together with :421-535.  gs_part of padding rows is unspecified (nothing reads it). */
+int momoe_dgrad2_swiglu_bwd_tokens(const momoe_plan_t* plan, const void* g_MD, const void* W2_NHD,
+                                   const void* a_saved, const void* b_saved, const void* a_recomp,
+                                   const void* b_recomp, void* gz_sorted, void* hs_sorted, float* gs_part,
+                                   momoe_stream_t stream);
+
 /* gx_sorted = bf16(gz_sorted W1[e]^T).  Replaces the GEMM of momoe/momoe.py:612-681. */
 int momoe_dgrad1(const momoe_plan_t* plan, const void* gz_sorted, const void* W1_ND2H, void* gx_sorted,
                  momoe_stream_t stream);
@@ -165,6 +182,13 @@ int momoe_dgrad1(const momoe_plan_t* plan, const void* gz_sorted, const void* W1
  * A: [rows, X], B: [rows, Y] expert-major bf16.  Replaces momoe/momoe.py:356-412. */
 int momoe_wgrad(const momoe_plan_t* plan, const void* a_sorted, int32_t X, const void* b_sorted, int32_t Y,
                 void* dW_NXY, momoe_stream_t stream);
+
+/* momoe_wgrad with either operand token-major: when a_is_token_major (b_is_token_major) is non-zero, `a` (`b`) is a
+ * bf16 [plan->M, X] ([plan->M, Y]) matrix whose rows are fetched through plan->row_token; the other operand must be
+ * expert-major with zero padding rows (hs_sorted and gz_sorted are).  Replaces momoe/momoe.py:356-412 fed by the
+ * gathers of :298-350. */
+int momoe_wgrad_tokens(const momoe_plan_t* plan, const void* a, int32_t X, int32_t a_is_token_major, const void* b,
+                       int32_t Y, int32_t b_is_token_major, void* dW_NXY, momoe_stream_t stream);
 
 /* Dense G_s_NM fp32 [N,M] contiguous (zero where unselected) from the per-row partial sums.
  * Replaces the zero-init + atomics of momoe/momoe.py:721,699-703. */
@@ -200,6 +224,12 @@ int momoe_bias_update(float* biases_N, const int64_t* sizes_N, int32_t N, int32_
  * (entry [rank] is the local one).  The flag arrays (uint32[8] per rank) must start zeroed; `epoch` must grow by one
  * with every hand-shake, identically on every rank.  Waits on a peer are bounded (status 301 when they run out).
  * ------------------------------------------------------------------------------------------------------------ */
+
+/* Limit of every wait on a peer's flag, in SM clock cycles (default 4e9, about two seconds); values <= 0 leave it
+ * unchanged.  Returns the previous limit.  A process-wide host-side setting, read when a hand-shake is launched.  A
+ * wait that runs out writes status 301 and the kernel returns normally; once 301 is recorded momoe_ep_dispatch_rows
+ * sends nothing. */
+int64_t momoe_ep_set_wait_limit(int64_t sm_cycles);
 
 /* Store this rank's per-expert token counts (sizes_N of momoe_build_permutation) into row `rank` of every peer's
  * int32[R*N] counts matrix, then hand-shake: on return (in stream order) this rank's matrix is complete. */

@@ -25,7 +25,10 @@
 namespace momoe {
 
 constexpr int EP_MAX_RANKS = 8;
-constexpr long long kFlagWaitCycles = 4000000000LL;   // about two seconds of SM clocks
+constexpr long long kFlagWaitCyclesDefault = 4000000000LL;   // about two seconds of SM clocks
+// Limit of every wait on a peer's flag, in SM clock cycles; a host-side setting read at launch time
+// (momoe_ep_set_wait_limit).  Always finite.
+static long long g_flag_wait_cycles = kFlagWaitCyclesDefault;
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -39,7 +42,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // Thread s < world: tell peer s that this rank reached `epoch`, then wait until peer s has told us the same.
 // flags[p] points at rank p's flag array; slot [r] of it is written by rank r only.
 __device__ __forceinline__ void flag_handshake(uint32_t* const* flags, int world, int rank, uint32_t epoch,
-                                               int* status) {
+                                               int* status, long long wait_cycles) {
     __threadfence_system();
     __syncthreads();
     const int s = threadIdx.x;
@@ -49,7 +52,7 @@ __device__ __forceinline__ void flag_handshake(uint32_t* const* flags, int world
         const long long t0 = clock64();
         // epochs only grow; the signed difference tolerates wrap-around
         while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
-            if (clock64() - t0 > kFlagWaitCycles) {
+            if (clock64() - t0 > wait_cycles) {
                 atomicCAS(status, 0, DEV_TIMEOUT_PEER);
                 break;
             }
@@ -64,16 +67,17 @@ struct PeerPtrs {
 };
 
 __global__ void ep_publish_counts_kernel(const long long* __restrict__ sizes_N, int N, PeerPtrs counts, PeerPtrs flags,
-                                         int world, int rank, uint32_t epoch, int* status) {
+                                         int world, int rank, uint32_t epoch, int* status, long long wait_cycles) {
     for (int e = threadIdx.x; e < N; e += blockDim.x) {
         const int v = static_cast<int>(sizes_N[e]);
         for (int p = 0; p < world; ++p) static_cast<int*>(counts.p[p])[rank * N + e] = v;
     }
-    flag_handshake(reinterpret_cast<uint32_t* const*>(flags.p), world, rank, epoch, status);
+    flag_handshake(reinterpret_cast<uint32_t* const*>(flags.p), world, rank, epoch, status, wait_cycles);
 }
 
-__global__ void ep_barrier_kernel(PeerPtrs flags, int world, int rank, uint32_t epoch, int* status) {
-    flag_handshake(reinterpret_cast<uint32_t* const*>(flags.p), world, rank, epoch, status);
+__global__ void ep_barrier_kernel(PeerPtrs flags, int world, int rank, uint32_t epoch, int* status,
+                                  long long wait_cycles) {
+    flag_handshake(reinterpret_cast<uint32_t* const*>(flags.p), world, rank, epoch, status, wait_cycles);
 }
 
 // One block.  counts_RN[s*N + e] = tokens rank s routes to global expert e.
@@ -173,7 +177,10 @@ ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ h
                         const float* __restrict__ home_row_weight, const int* __restrict__ dst_base, int Nl,
                         int vec_per_row, PeerPtrs rows, PeerPtrs row_w, int* __restrict__ remote_row, int rank,
                         int world, const int* __restrict__ local_count, const int* __restrict__ local_pad_off,
-                        bool wide) {
+                        bool wide, const int* __restrict__ status) {
+    // a hand-shake that timed out leaves counts and plans that cannot be trusted: no payload is sent then; like an
+    // overflow (302, dst_base = -1) the rows still get an in-range remote_row so that later reads stay inside the buffers
+    const bool no_send = status != nullptr && *reinterpret_cast<const volatile int*>(status) == DEV_TIMEOUT_PEER;
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
     const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -195,8 +202,8 @@ ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ h
         const int tok = home_row_token[pr];
         if (tok < 0) continue;
         const int e = home_tile_expert[pr / TILE_M];
-        const int base = dst_base[e];
-        if (base < 0) {   // capacity exceeded somewhere: nothing is sent (the status word already records it)
+        const int base = no_send ? -1 : dst_base[e];
+        if (base < 0) {   // capacity exceeded somewhere, or a peer is missing: nothing is sent (the status word records it)
             if (lane == 0 && remote_row != nullptr) remote_row[pr] = 0;   // keep later reads inside the buffers
             continue;
         }
@@ -342,6 +349,12 @@ using namespace momoe;
 #define EP_LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? MOMOE_OK : MOMOE_ERR_CUDA)
 #define EP_API extern "C" __attribute__((visibility("default")))
 
+EP_API int64_t momoe_ep_set_wait_limit(int64_t sm_cycles) {
+    const long long before = g_flag_wait_cycles;
+    if (sm_cycles > 0) g_flag_wait_cycles = sm_cycles;
+    return before;
+}
+
 EP_API int momoe_ep_publish_counts(const int64_t* sizes_N, int32_t N, void* const* peer_counts,
                                    void* const* peer_flags, int32_t world, int32_t rank, uint32_t epoch,
                                    int32_t* status, momoe_stream_t stream) {
@@ -352,7 +365,7 @@ EP_API int momoe_ep_publish_counts(const int64_t* sizes_N, int32_t N, void* cons
     if (fill_peers(c, peer_counts, world) != MOMOE_OK || fill_peers(f, peer_flags, world) != MOMOE_OK)
         return MOMOE_ERR_ARG;
     ep_publish_counts_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const long long*>(sizes_N), N, c, f, world, rank, epoch, status);
+        reinterpret_cast<const long long*>(sizes_N), N, c, f, world, rank, epoch, status, g_flag_wait_cycles);
     return EP_LAUNCH_OK();
 }
 
@@ -362,7 +375,8 @@ EP_API int momoe_ep_barrier(void* const* peer_flags, int32_t world, int32_t rank
     if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world) return MOMOE_ERR_ARG;
     PeerPtrs f;
     if (fill_peers(f, peer_flags, world) != MOMOE_OK) return MOMOE_ERR_ARG;
-    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, world, rank, epoch, status);
+    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, world, rank, epoch, status,
+                                                                        g_flag_wait_cycles);
     return EP_LAUNCH_OK();
 }
 
@@ -402,7 +416,8 @@ EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int
     const bool wide = (cols % 16 == 0) && (align & 31) == 0;   // 256-bit stores need 32-byte aligned rows
     ep_dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(src), home->row_token, home->tile_expert, home->pad_off, home->row_weight,
-        dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, world, local_count, local_pad_off, wide);
+        dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, world, local_count, local_pad_off, wide,
+        home->status);
     return EP_LAUNCH_OK();
 }
 

@@ -8,10 +8,12 @@
 // one thread of the leader CTA issues M=256 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives
 // its 128 rows x 256 columns.  Every TMA load has exactly one destination CTA.
 //
-// CTA = 320 threads: warp 0 (one lane) issues TMA loads, warp 1 allocates TMEM and (leader CTA, one lane) issues
-// the MMAs, warps 2..9 read accumulators out of TMEM and write the results.  A warp may only read the 32 TMEM lanes
-// of its quarter (warp_id % 4), so two warps share each quarter and split the tile's columns in halves.  Two
-// accumulator buffers in TMEM (2 x 256 columns) let the epilogue of one tile overlap the main loop of the next.
+// CTA = 320 threads: warp 0 issues TMA loads (one lane; all 32 lanes when an operand's rows are fetched by token id
+// with row-gather loads), warp 1 allocates TMEM and (leader CTA, one lane) issues the MMAs, warps 2..9 read
+// accumulators out of TMEM, convert them and hand them to TMA stores through a 4 KiB staging area per warp.  A warp may
+// only read the 32 TMEM lanes of its quarter (warp_id % 4), so two warps share each quarter and split the tile's
+// columns in halves.  Two accumulator buffers in TMEM (2 x 256 columns) let the epilogue of one tile overlap the
+// main loop of the next.
 //
 // Barriers (mbarrier in shared memory):
 //   full[s]      leader only; the leader's producer arms it with the bytes of BOTH CTAs, both CTAs' loads credit it
@@ -26,8 +28,6 @@
 //                    one MMA (k = 16) advances the start address by 32 bytes.
 //   MN-major operand two [64 k x 64 mn] boxes of 8 KiB: k-row at byte k*128, boxes 8192 bytes apart;
 //                    descriptor LBO = 8192 (mn pitch), SBO = 1024 (8-k group pitch); one MMA advances 2048 bytes.
-#include <cstdio>
-#include <cstdlib>
 #include <cstring>
 
 #include "internal.h"
@@ -47,7 +47,8 @@ constexpr int HALF_BYTES = A_BYTES + B_BYTES;        // one 64-wide k slice
 constexpr int KB = 2 * TILE_K;
 constexpr int STAGE_BYTES = 2 * HALF_BYTES;
 constexpr int STAGES = 3;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
+constexpr int EPI_WARP_BYTES = 4096;                     // staging area of one epilogue warp (results -> TMA stores)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_WARPS * EPI_WARP_BYTES + 1024;  // + slack for 1024-byte alignment
 constexpr int ACC_BUFS = 2;
 constexpr int TMEM_COLS = 512;
 
@@ -76,14 +77,13 @@ struct GemmArgs {
     const __nv_bfloat16* a_recomp;
     const __nv_bfloat16* b_recomp;
     float* gs_part;
-    uint32_t dbg;    // debug builds only: bit 0 skip epilogue stores, bit 1 skip epilogue math, bit 2 skip MMA
+    // Rows fetched straight from a token-major matrix instead of an expert-major copy: `rows` (the plan's row_token
+    // table) gives the token of every padded row, `gather` says which operand is addressed through it (bit 0: A,
+    // bit 1: B, wgrad only), `n_tokens` bounds the indices.
+    const int* rows;
+    int gather;
+    int n_tokens;
 };
-
-#ifdef MOMOE_DEBUG_KNOBS
-#define DBG(g, bit) (((g).dbg >> (bit)) & 1u)
-#else
-#define DBG(g, bit) 0u
-#endif
 
 template <int MODE>
 struct Cfg {
@@ -102,58 +102,11 @@ __device__ __forceinline__ void unpack_bf16(uint32_t v, float& lo, float& hi) {
 }
 __device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
-// Store 32 consecutive fp32 values as bf16 to dst (16-byte aligned), keeping only columns < ncols_left.
-// ncols_left is a multiple of 8 by contract (all matrix widths are).
-__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float (&v)[32], int ncols_left) {
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-        if (g * 8 < ncols_left) {
-            uint4 q;
-            q.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
-            q.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
-            q.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
-            q.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
-            *reinterpret_cast<uint4*>(dst + g * 8) = q;
-        }
-    }
-}
-// 256-bit global accesses (one full 32-byte sector per thread): half as many load/store instructions, which
-// matters because the row-per-thread pattern of the epilogues costs one tag look-up per thread and instruction.
-__device__ __forceinline__ void st_global_256(void* p, const uint32_t (&v)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
-                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
-                 : "memory");
-}
+// 256-bit global loads (one full 32-byte sector per thread) for the a,b rows the dgrad-2 epilogue reads.
 __device__ __forceinline__ void ld_global_nc_256(const void* p, uint32_t (&v)[8]) {
     asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                  : "l"(p));
-}
-// Same as store_row32 for rows whose pitch is a multiple of 32 bytes and a fully valid 32-column chunk.
-__device__ __forceinline__ void store_row32_wide(__nv_bfloat16* dst, const float (&v)[32]) {
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-        uint32_t q[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = pack_bf16(v[g * 16 + 2 * j], v[g * 16 + 2 * j + 1]);
-        st_global_256(dst + g * 16, q);
-    }
-}
-__device__ __forceinline__ void store_row32_auto(__nv_bfloat16* dst, const float (&v)[32], int ncols_left, bool wide) {
-    if (wide && ncols_left >= 32) store_row32_wide(dst, v);
-    else store_row32(dst, v, ncols_left);
-}
-// Load 32 consecutive bf16 values (16-byte aligned) as fp32; columns >= ncols_left read as zero.
-__device__ __forceinline__ void load_row32(const __nv_bfloat16* src, float (&v)[32], int ncols_left) {
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-        uint4 q = make_uint4(0, 0, 0, 0);
-        if (g * 8 < ncols_left) q = __ldg(reinterpret_cast<const uint4*>(src + g * 8));
-        unpack_bf16(q.x, v[g * 8 + 0], v[g * 8 + 1]);
-        unpack_bf16(q.y, v[g * 8 + 2], v[g * 8 + 3]);
-        unpack_bf16(q.z, v[g * 8 + 4], v[g * 8 + 5]);
-        unpack_bf16(q.w, v[g * 8 + 6], v[g * 8 + 7]);
-    }
 }
 
 // Work item -> coordinates of THIS CTA.
@@ -202,7 +155,8 @@ __device__ __forceinline__ Work decode_work(const GemmArgs& g, int item, uint32_
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmArgs g) {
+                    const __grid_constant__ CUtensorMap tmO0, const __grid_constant__ CUtensorMap tmO1,
+                    const __grid_constant__ CUtensorMap tmO2, const GemmArgs g) {
     using C = Cfg<MODE>;
 
     extern __shared__ uint8_t smem_raw[];
@@ -220,11 +174,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int cluster_id = blockIdx.x >> 1;
     const int n_clusters = gridDim.x >> 1;
     const uint32_t stage_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-#ifdef MOMOE_DEBUG_KNOBS
-    long long dbg_c0 = clock64();
-    unsigned long long dbg_t0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(dbg_t0));
-#endif
 
     // ---- work range (device-resident schedule; nothing is read back by the host)
     int total_items;
@@ -245,6 +194,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         fence_mbar_init();
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
+        tma_prefetch_desc(&tmO0);
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(&tmem_slot), TMEM_COLS);
@@ -257,7 +207,107 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
     volatile int* abortp = &abort_flag;
 
-    if (warp == 0) {
+    if (warp == 0 && g.gather != 0) {
+        // ================================================================ TMA producer, rows gathered by token id
+        // The whole warp works: lane 0 waits for the stage and issues the tiled loads of the operand that is not
+        // gathered; every lane issues the row-gather loads of four rows of the gathered operand per 64-wide slice.
+        // Padding rows (token -1) repeat the first row of their 128-row tile, which is always a real row of the same
+        // expert: every consumer multiplies them by a zero routing weight or by the zero padding rows of the other
+        // operand.
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint32_t full0 = mapa_shared(smem_u32(&bar_full[0]), 0);   // the leader's barriers
+        const int r = static_cast<int>(cta_rank);
+        const unsigned n_tok = static_cast<unsigned>(g.n_tokens);
+        auto fix = [&](int4& t, int first) {
+            t.x = static_cast<unsigned>(t.x) < n_tok ? t.x : first;
+            t.y = static_cast<unsigned>(t.y) < n_tok ? t.y : first;
+            t.z = static_cast<unsigned>(t.z) < n_tok ? t.z : first;
+            t.w = static_cast<unsigned>(t.w) < n_tok ? t.w : first;
+        };
+        for (int item = cluster_id; ok && item < total_items; item += n_clusters) {
+            const Work w = decode_work<MODE>(g, item, cta_rank);
+            if (w.skip) continue;
+            int4 tok = make_int4(0, 0, 0, 0);
+            if constexpr (MODE != MODE_WGRAD) {
+                // rows 4*lane .. 4*lane+3 of this CTA's tile; a CTA whose half of the pair is missing loads its
+                // partner's rows again (its accumulator is never stored)
+                const int t_src = w.valid ? w.tile : w.tile - 1;
+                tok = __ldg(reinterpret_cast<const int4*>(g.rows + static_cast<size_t>(t_src) * TILE_M) + lane);
+                int first = __shfl_sync(0xffffffffu, tok.x, 0);
+                first = static_cast<unsigned>(first) < n_tok ? first : 0;
+                fix(tok, first);
+            }
+            for (int kb = 0; kb < w.nkb; ++kb) {
+                int4 tk[2];
+                if constexpr (MODE == MODE_WGRAD) {
+                    // contraction rows of this k-block: lanes l and l+16 fetch the same four rows for the two
+                    // 64-column boxes of the slice; the loads are in flight while lane 0 waits for the stage
+                    const int rbase = w.row0 + kb * KB;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        tk[h] = __ldg(reinterpret_cast<const int4*>(g.rows + rbase + h * TILE_K) + (lane & 15));
+                    int first = __shfl_sync(0xffffffffu, tk[0].x, 0);
+                    first = static_cast<unsigned>(first) < n_tok ? first : 0;
+                    fix(tk[0], first);
+                    fix(tk[1], first);
+                }
+                int okw = 1;
+                if (lane == 0)
+                    okw = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, g.status, DEV_TIMEOUT_PRODUCER)
+                              ? 1 : 0;
+                okw = __shfl_sync(0xffffffffu, okw, 0);
+                if (okw == 0) { ok = false; break; }
+                const uint32_t full = full0 + static_cast<uint32_t>(stage * sizeof(uint64_t));
+                if (lane == 0 && leader) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2 * STAGE_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t sa = stage_base + stage * STAGE_BYTES + h * HALF_BYTES;
+                    const uint32_t sb = sa + A_BYTES;
+                    const int k0 = kb * KB + h * TILE_K;
+                    if constexpr (MODE == MODE_WGRAD) {
+                        const int r0 = w.row0 + k0;
+                        const int i = lane >> 4;          // which 64-column box of the slice
+                        const uint32_t off = i * 8192 + (lane & 15) * 512;
+                        if (g.gather & 1)
+                            tma_gather4_pair(sa + off, &tmA, full, w.mb * 256 + r * 128 + i * 64, tk[h].x, tk[h].y,
+                                             tk[h].z, tk[h].w);
+                        if (g.gather & 2)
+                            tma_gather4_pair(sb + off, &tmB, full, w.nb * PAIR_N + r * 128 + i * 64, tk[h].x, tk[h].y,
+                                             tk[h].z, tk[h].w);
+                        if (lane == 0) {
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                if (!(g.gather & 1))
+                                    tma_load_2d_pair(sa + j * 8192, &tmA, full, w.mb * 256 + r * 128 + j * 64, r0);
+                                if (!(g.gather & 2))
+                                    tma_load_2d_pair(sb + j * 8192, &tmB, full, w.nb * PAIR_N + r * 128 + j * 64, r0);
+                            }
+                        }
+                    } else {
+                        tma_gather4_pair(sa + lane * 512, &tmA, full, k0, tok.x, tok.y, tok.z, tok.w);
+                        if (lane == 0) {
+                            if constexpr (MODE == MODE_UP) {
+#pragma unroll
+                                for (int i = 0; i < 2; ++i)
+                                    tma_load_3d_pair(sb + i * 8192, &tmB, full, r * g.half + w.nb * 128 + i * 64, k0,
+                                                     w.e);
+                            } else if constexpr (MODE == MODE_DOWN) {
+#pragma unroll
+                                for (int i = 0; i < 2; ++i)
+                                    tma_load_3d_pair(sb + i * 8192, &tmB, full, w.nb * PAIR_N + r * 128 + i * 64, k0,
+                                                     w.e);
+                            } else {
+                                tma_load_3d_pair(sb, &tmB, full, k0, w.nb * PAIR_N + r * 128, w.e);
+                            }
+                        }
+                    }
+                }
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 0) {
         // ================================================================ TMA producer (both CTAs)
         if (lane == 0) {
             int stage = 0;
@@ -269,11 +319,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 for (int kb = 0; kb < w.nkb; ++kb) {
                     ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, g.status, DEV_TIMEOUT_PRODUCER);
                     if (!ok) break;
-                    if (DBG(g, 4)) {   // debug: no loads at all, the MMAs run on whatever shared memory holds
-                        if (leader) mbar_arrive(smem_u32(&bar_full[stage]));
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                        continue;
-                    }
                     if (leader) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2 * STAGE_BYTES);
                     const uint32_t full = mapa_shared(smem_u32(&bar_full[stage]), 0);   // the leader's barrier
                     const int r = static_cast<int>(cta_rank);
@@ -346,14 +391,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 for (int kb = 0; kb < w.nkb; ++kb) {
                     ok = mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, g.status, DEV_TIMEOUT_MMA);
                     if (!ok) break;
-                    if (!DBG(g, 2)) {
-                        umma_bf16_pair_lohi(tmem_d, a_lo, desc_hi, b_lo, desc_hi, idesc, kb != 0 ? 1u : 0u);
+                    umma_bf16_pair_lohi(tmem_d, a_lo, desc_hi, b_lo, desc_hi, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-                        for (uint32_t k = 1; k < (DBG(g, 6) ? 1u : 2u * TILE_K / UMMA_K); ++k) {
-                            const uint32_t off = (k >> 2) * (HALF_BYTES >> 4);   // second 64-wide slice of the stage
-                            umma_bf16_pair_lohi(tmem_d, a_lo + off + (k & 3u) * a_kstep, desc_hi,
-                                                b_lo + off + (k & 3u) * b_kstep, desc_hi, idesc, 1u);
-                        }
+                    for (uint32_t k = 1; k < 2u * TILE_K / UMMA_K; ++k) {
+                        const uint32_t off = (k >> 2) * (HALF_BYTES >> 4);   // second 64-wide slice of the stage
+                        umma_bf16_pair_lohi(tmem_d, a_lo + off + (k & 3u) * a_kstep, desc_hi,
+                                            b_lo + off + (k & 3u) * b_kstep, desc_hi, idesc, 1u);
                     }
                     umma_commit_pair(smem_u32(&bar_empty[stage]), 3);  // frees the stage in both CTAs
                     a_lo += STAGE_BYTES >> 4;
@@ -372,11 +415,61 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     } else {
         // ================================================================ epilogue (warps 2..9, both CTAs)
+        // Results leave through shared memory: a warp converts its 32 rows x 32 (dgrad-2: 16) columns to bf16, writes
+        // them into a slot of its 4 KiB staging area in the swizzled layout of the output's tensor map, and one lane
+        // hands the slot to a TMA store.  Global memory then sees full 64-byte (32-byte) row pieces written by the copy
+        // engine instead of one 32-byte access per thread and row, and tails (columns past the matrix width, rows past
+        // an expert's weight matrix) are clipped by the tensor map.  Slots rotate; a slot is rewritten once the store
+        // issued from it has finished READING it.
         const int q = warp & 3;            // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;     // accumulator row == TMEM lane
         const int half = (warp - 2) >> 2;  // which half of the tile's 32-column chunks this warp handles
         const uint32_t acc_empty_leader = mapa_shared(smem_u32(&bar_acc_empty[0]), 0);
-        const bool wide = (g.out_cols % 16) == 0;   // every row of the outputs starts on a 32-byte boundary
+        constexpr int SLOT_BYTES = MODE == MODE_DGRAD2 ? 1024 : 2048;
+        constexpr int NSLOTS = EPI_WARP_BYTES / SLOT_BYTES;
+        const uint32_t stage_area = stage_base + STAGES * STAGE_BYTES + (warp - 2) * EPI_WARP_BYTES;
+        int n_stored = 0;                  // pieces handed to TMA stores so far (lane 0 owns the bulk groups)
+        // slot for the next piece, free to write
+        auto slot_acquire = [&]() -> uint32_t {
+            if (n_stored >= NSLOTS && lane == 0) bulk_wait_read<NSLOTS - 1>();
+            __syncwarp();
+            return stage_area + (n_stored % NSLOTS) * SLOT_BYTES;
+        };
+        // 32 columns of this thread's row (16 packed bf16 pairs) into a [32 rows x 64 bytes] slot, 64-byte swizzle:
+        // 16-byte chunk j of row r sits at chunk position j ^ ((r >> 1) & 3)
+        auto slot_write64 = [&](uint32_t slot, const uint32_t (&p)[16]) {
+            const uint32_t base = slot + lane * 64;
+            const uint32_t x = (lane >> 1) & 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                st_shared_v4(base + ((j ^ x) << 4), p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+        };
+        // 16 columns (8 pairs) into a [32 rows x 32 bytes] slot, 32-byte swizzle: chunk j of row r at j ^ ((r >> 2) & 1)
+        auto slot_write32 = [&](uint32_t slot, const uint32_t (&p)[8]) {
+            const uint32_t base = slot + lane * 32;
+            const uint32_t x = (lane >> 2) & 1;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                st_shared_v4(base + ((j ^ x) << 4), p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+        };
+        auto slot_store2d = [&](const CUtensorMap* tm, uint32_t slot, int c0, int c1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tm, slot, c0, c1);
+                bulk_commit();
+            }
+            ++n_stored;
+        };
+        auto slot_store3d = [&](const CUtensorMap* tm, uint32_t slot, int c0, int c1, int c2) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(tm, slot, c0, c1, c2);
+                bulk_commit();
+            }
+            ++n_stored;
+        };
         int it = 0;
         bool ok = true;
         for (int item = cluster_id; ok && item < total_items; item += n_clusters) {
@@ -386,12 +479,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t aphase = (it >> 1) & 1u;
             ++it;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * PAIR_N;
+            const int row0 = w.tile * TILE_M + q * 32;   // first of this warp's 32 output rows (row-tile modes)
             uint32_t r[32];
             if constexpr (MODE == MODE_DGRAD2) {
                 // The saved / recomputed a,b rows do not depend on the accumulator: the first 32-column chunk is
                 // fetched while the main loop is still running, each later chunk while the previous one is computed.
                 const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
                 const int H = g.out_cols;
+                const bool wide = (H % 16) == 0;   // every a,b row starts on a 32-byte boundary
                 const int n_saved = __ldg(g.sched + SCHED_N_SAVED_TILES);
                 const bool saved = w.tile < n_saved;
                 const size_t abrow =
@@ -432,18 +527,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll 1
                     for (int c = c_begin; c < c_end; ++c) {
                         const int col0 = w.nb * PAIR_N + c * 32;
-                        const int left = H - col0;
-                        if (left <= 0) break;
+                        if (col0 >= H) break;
                         uint4 ca[4], cb[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) { ca[i] = na[i]; cb[i] = nb4[i]; }
                         if (c + 1 < c_end) fetch(c + 1);
                         tmem_ld32(taddr + c * 32, r);
                         tmem_ld_wait();
-                        __nv_bfloat16* z1p = g.out0 + grow * (2 * H) + col0;
-                        __nv_bfloat16* hsp = g.out1 + grow * H + col0;
 #pragma unroll
-                        for (int i2 = 0; i2 < 2; ++i2) {   // 16 columns at a time: compute, pack, store
+                        for (int i2 = 0; i2 < 2; ++i2) {   // 16 columns at a time: compute, pack, stage, store
                             uint32_t o1[8], o2[8], o3[8];
 #pragma unroll
                             for (int ii = 0; ii < 2; ++ii) {
@@ -468,25 +560,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                     o3[ii * 4 + j] = pack_bf16(wgt * h0, wgt * h1);
                                 }
                             }
-                            if (DBG(g, 0)) continue;
-                            if (wide && left >= 32) {
-                                st_global_256(z1p + i2 * 16, o1);
-                                st_global_256(z1p + H + i2 * 16, o2);
-                                st_global_256(hsp + i2 * 16, o3);
-                            } else {
-#pragma unroll
-                                for (int ii = 0; ii < 2; ++ii) {
-                                    const int i = i2 * 2 + ii;
-                                    if (i * 8 < left) {
-                                        *reinterpret_cast<uint4*>(z1p + i * 8) =
-                                            make_uint4(o1[ii * 4], o1[ii * 4 + 1], o1[ii * 4 + 2], o1[ii * 4 + 3]);
-                                        *reinterpret_cast<uint4*>(z1p + H + i * 8) =
-                                            make_uint4(o2[ii * 4], o2[ii * 4 + 1], o2[ii * 4 + 2], o2[ii * 4 + 3]);
-                                        *reinterpret_cast<uint4*>(hsp + i * 8) =
-                                            make_uint4(o3[ii * 4], o3[ii * 4 + 1], o3[ii * 4 + 2], o3[ii * 4 + 3]);
-                                    }
-                                }
-                            }
+                            const int col = col0 + i2 * 16;
+                            if (col >= H) continue;   // uniform across the warp
+                            // gz is addressed as [rows, 2, H] so that the linear half is clipped at H
+                            uint32_t slot = slot_acquire();
+                            slot_write32(slot, o1);
+                            slot_store3d(&tmO0, slot, col, 0, row0);
+                            slot = slot_acquire();
+                            slot_write32(slot, o2);
+                            slot_store3d(&tmO0, slot, col, 1, row0);
+                            slot = slot_acquire();
+                            slot_write32(slot, o3);
+                            slot_store2d(&tmO1, slot, col, row0);
                         }
                     }
                     g.gs_part[(grow * g.n_nblk + w.nb) * 2 + half] = gs;   // two partial sums per 256-column block
@@ -502,79 +587,90 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ok = mbar_wait(smem_u32(&bar_acc_full[ab]), aphase, abortp, g.status, DEV_TIMEOUT_EPILOGUE);
             if (!ok) break;
             tc_fence_after();
-            float v[32];
+            uint32_t p[16];
 
-            if (DBG(g, 5)) {
-                // debug: handshake only
-            } else if constexpr (MODE == MODE_UP) {
-                const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
+            if constexpr (MODE == MODE_UP) {
                 const int n_saved = __ldg(g.sched + SCHED_N_SAVED_TILES);
                 const bool store_ab = (g.ab_mode == 1 && w.tile < n_saved) || (g.ab_mode == 2 && w.tile >= n_saved);
-                const size_t abrow =
-                    (g.ab_mode == 2 ? static_cast<size_t>(w.tile - n_saved) : static_cast<size_t>(w.tile)) * TILE_M + row;
+                const int abrow0 = (g.ab_mode == 2 ? w.tile - n_saved : w.tile) * TILE_M + q * 32;
                 if (w.valid) {
 #pragma unroll 1
                     for (int c = half * 2; c < half * 2 + 2; ++c) {
                         const int col0 = w.nb * 128 + c * 32;
-                        const int left = g.out_cols - col0;
-                        if (left <= 0) break;   // uniform across the warp
-                        float a[32], b[32];
+                        if (col0 >= g.out_cols) break;   // uniform across the warp
+                        float a[32];
                         tmem_ld32(taddr + c * 32, r);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) a[i] = __uint_as_float(r[i]);
                         tmem_ld32(taddr + 128 + c * 32, r);
                         tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) b[i] = __uint_as_float(r[i]);
                         if (store_ab) {
-                            store_row32_auto(g.out1 + abrow * g.out_cols + col0, a, DBG(g, 0) ? 0 : left, wide);
-                            store_row32_auto(g.out2 + abrow * g.out_cols + col0, b, DBG(g, 0) ? 0 : left, wide);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) p[i] = pack_bf16(a[2 * i], a[2 * i + 1]);
+                            uint32_t slot = slot_acquire();
+                            slot_write64(slot, p);
+                            slot_store2d(&tmO1, slot, col0, abrow0);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                p[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                            slot = slot_acquire();
+                            slot_write64(slot, p);
+                            slot_store2d(&tmO2, slot, col0, abrow0);
                         }
                         if (g.out0 != nullptr) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = b[i] * sigmoidf_fast(b[i]) * a[i];
-                            store_row32_auto(g.out0 + grow * g.out_cols + col0, v, DBG(g, 0) ? 0 : left, wide);
+                            for (int i = 0; i < 16; ++i) {
+                                const float b0 = __uint_as_float(r[2 * i]), b1 = __uint_as_float(r[2 * i + 1]);
+                                p[i] = pack_bf16(b0 * sigmoidf_fast(b0) * a[2 * i], b1 * sigmoidf_fast(b1) * a[2 * i + 1]);
+                            }
+                            const uint32_t slot = slot_acquire();
+                            slot_write64(slot, p);
+                            slot_store2d(&tmO0, slot, col0, row0);
                         }
                     }
                 }
             } else if constexpr (MODE == MODE_DOWN || MODE == MODE_DGRAD1) {
-                const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
                 if (w.valid) {
                     float wgt = 1.0f;
-                    if constexpr (MODE == MODE_DOWN) wgt = __ldg(g.row_weight + grow);
+                    if constexpr (MODE == MODE_DOWN) wgt = __ldg(g.row_weight + static_cast<size_t>(w.tile) * TILE_M + row);
 #pragma unroll 1
                     for (int c = half * 4; c < half * 4 + 4; ++c) {
                         const int col0 = w.nb * PAIR_N + c * 32;
-                        const int left = g.out_cols - col0;
-                        if (left <= 0) break;
+                        if (col0 >= g.out_cols) break;
                         tmem_ld32(taddr + c * 32, r);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * wgt;
-                        store_row32_auto(g.out0 + grow * g.out_cols + col0, v, DBG(g, 0) ? 0 : left, wide);
+                        for (int i = 0; i < 16; ++i)
+                            p[i] = pack_bf16(__uint_as_float(r[2 * i]) * wgt, __uint_as_float(r[2 * i + 1]) * wgt);
+                        const uint32_t slot = slot_acquire();
+                        slot_write64(slot, p);
+                        slot_store2d(&tmO0, slot, col0, row0);
                     }
                 }
             } else if constexpr (MODE == MODE_DGRAD2) {
-                // handled below: its operand prefetch starts before the accumulator wait
+                // handled above: its operand prefetch starts before the accumulator wait
             } else {  // MODE_WGRAD
-                const int orow = w.mb * 256 + static_cast<int>(cta_rank) * TILE_M + row;
-                __nv_bfloat16* dst = g.out0 + (static_cast<size_t>(w.e) * g.out_rows + orow) * g.out_cols;
+                const int orow0 = w.mb * 256 + static_cast<int>(cta_rank) * TILE_M + q * 32;
+                if (orow0 < g.out_rows) {   // rows past the matrix inside the box are clipped by the tensor map
 #pragma unroll 1
-                for (int c = half * 4; c < half * 4 + 4; ++c) {
-                    const int col0 = w.nb * PAIR_N + c * 32;
-                    const int left = g.out_cols - col0;
-                    if (left <= 0) break;
-                    if (w.nkb > 0) {
-                        tmem_ld32(taddr + c * 32, r);
-                        tmem_ld_wait();
+                    for (int c = half * 4; c < half * 4 + 4; ++c) {
+                        const int col0 = w.nb * PAIR_N + c * 32;
+                        if (col0 >= g.out_cols) break;
+                        if (w.nkb > 0) {
+                            tmem_ld32(taddr + c * 32, r);
+                            tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                    } else {
+                            for (int i = 0; i < 16; ++i)
+                                p[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                            for (int i = 0; i < 16; ++i) p[i] = 0u;
+                        }
+                        const uint32_t slot = slot_acquire();
+                        slot_write64(slot, p);
+                        slot_store3d(&tmO0, slot, col0, orow0, w.e);
                     }
-                    if (orow < g.out_rows) store_row32_auto(dst + col0, v, DBG(g, 0) ? 0 : left, wide);
                 }
             }
             // hand the accumulator buffer back to the MMA thread of the leader CTA
@@ -585,6 +681,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 else mbar_arrive_cluster(acc_empty_leader + ab * static_cast<uint32_t>(sizeof(uint64_t)));
             }
         }
+        // the staging area must outlive every store issued from it
+        if (lane == 0) bulk_wait_all<0>();
+        __syncwarp();
     }
 
     // ---- teardown: both CTAs meet (the peer's shared memory and TMEM stay alive until the leader's last MMA has
@@ -601,14 +700,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
-#ifdef MOMOE_DEBUG_KNOBS
-    if (DBG(g, 3) && blockIdx.x == 0 && threadIdx.x == 0) {
-        unsigned long long t1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        const long long dc = clock64() - dbg_c0;
-        printf("mode %d: %lld cycles in %llu ns = %.0f MHz\n", MODE, dc, t1 - dbg_t0, 1e3 * dc / double(t1 - dbg_t0));
-    }
-#endif
 }
 
 // ---------------------------------------------------------------------------------------------- host side
@@ -631,9 +722,6 @@ static void base_args(const momoe_plan_t* p, GemmArgs& g) {
     g.status = p->status;
     g.n_experts = p->N;
     g.row_weight = p->row_weight;
-#ifdef MOMOE_DEBUG_KNOBS
-    if (const char* s = getenv("MOMOE_DEBUG_FLAGS")) g.dbg = static_cast<uint32_t>(atoi(s));
-#endif
 }
 
 // Number of CTA pairs that can be resident at once (the two CTAs of a pair sit on neighbouring SMs).
@@ -666,14 +754,31 @@ static int resident_pairs() {
     return cached[dev];
 }
 
+// Tensor maps of the (up to three) outputs of one launch; unused entries alias the first.
+struct OutMaps {
+    CUtensorMap m[3];
+    int n = 0;
+};
+// Output matrix [rows, cols] written in [32 rows x 32 columns] pieces (64-byte rows, 64-byte swizzle).
+static int out_map_2d(OutMaps& o, int i, void* base, uint64_t rows, uint64_t cols) {
+    return encode_tmap_2d(&o.m[i], base, rows, cols, 32, 32, TMAP_SWIZZLE_64B);
+}
+
 template <int MODE>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& g, cudaStream_t stream) {
-    // per-device attribute; setting it on every launch costs well under a microsecond of host time
-    if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-        cudaSuccess)
-        return MOMOE_ERR_CUDA;
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps& o, const GemmArgs& g,
+                  cudaStream_t stream) {
+    // the shared-memory attribute is per device and per function: set it the first time a device launches this mode
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return MOMOE_ERR_CUDA;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM_BYTES) != cudaSuccess)
+            return MOMOE_ERR_CUDA;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
     const int grid = 2 * resident_pairs<MODE>();
-    grouped_gemm_kernel<MODE><<<grid, CTA_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, g);
+    grouped_gemm_kernel<MODE><<<grid, CTA_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, o.m[0], o.m[1], o.m[2], g);
     return cudaGetLastError() == cudaSuccess ? MOMOE_OK : MOMOE_ERR_CUDA;
 }
 
@@ -683,22 +788,32 @@ static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 
 using namespace momoe;
 
-extern "C" __attribute__((visibility("default"))) int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted,
-                                                                     const void* W1_ND2H, void* h_sorted, void* a_out,
-                                                                     void* b_out, int32_t ab_mode,
-                                                                     momoe_stream_t stream) {
+// A operand of the row-tile modes: an expert-major matrix read in [128 x 64] boxes, or (tokens = true) the
+// token-major matrix [plan->M, cols] read four rows at a time through plan->row_token.
+static int a_operand(const momoe_plan_t* plan, const void* src, int cols, bool tokens, CUtensorMap* tm, GemmArgs& g) {
+    if (!tokens) return encode_tmap_2d(tm, src, plan->rows_capacity, cols, TILE_M, TILE_K);
+    // the row table is read four entries (16 bytes) at a time
+    if (plan->row_token == nullptr || (reinterpret_cast<uintptr_t>(plan->row_token) & 15) != 0) return MOMOE_ERR_ARG;
+    g.rows = plan->row_token;
+    g.gather = 1;
+    g.n_tokens = plan->M;
+    return encode_tmap_2d(tm, src, plan->M, cols, 1, TILE_K);
+}
+
+static int up_swiglu_impl(const momoe_plan_t* plan, const void* x, bool tokens, const void* W1_ND2H, void* h_sorted,
+                          void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
-    if (x_sorted == nullptr || W1_ND2H == nullptr) return MOMOE_ERR_ARG;
+    if (x == nullptr || W1_ND2H == nullptr) return MOMOE_ERR_ARG;
     if (ab_mode < 0 || ab_mode > 2) return MOMOE_ERR_ARG;
     if (ab_mode != 2 && h_sorted == nullptr) return MOMOE_ERR_ARG;
     if (ab_mode != 0 && (a_out == nullptr || b_out == nullptr)) return MOMOE_ERR_ARG;
     const int D = plan->D, H = plan->H;
     CUtensorMap tmA, tmB;
-    if ((rc = encode_tmap_2d(&tmA, x_sorted, plan->rows_capacity, D, TILE_M, TILE_K)) != MOMOE_OK) return rc;
-    if ((rc = encode_tmap_3d(&tmB, W1_ND2H, plan->N, D, 2 * H, TILE_K, 64)) != MOMOE_OK) return rc;
     GemmArgs g;
     base_args(plan, g);
+    if ((rc = a_operand(plan, x, D, tokens, &tmA, g)) != MOMOE_OK) return rc;
+    if ((rc = encode_tmap_3d(&tmB, W1_ND2H, plan->N, D, 2 * H, TILE_K, 64)) != MOMOE_OK) return rc;
     g.n_nblk = cdiv(H, 128);
     g.nkb = cdiv(D, KB);
     g.out_cols = H;
@@ -707,7 +822,27 @@ extern "C" __attribute__((visibility("default"))) int momoe_up_swiglu(const momo
     g.out0 = static_cast<__nv_bfloat16*>(h_sorted);
     g.out1 = static_cast<__nv_bfloat16*>(a_out);
     g.out2 = static_cast<__nv_bfloat16*>(b_out);
-    return launch<MODE_UP>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
+    OutMaps o;
+    o.m[0] = o.m[1] = o.m[2] = tmA;
+    if (h_sorted != nullptr && (rc = out_map_2d(o, 0, h_sorted, plan->rows_capacity, H)) != MOMOE_OK) return rc;
+    if (ab_mode != 0) {
+        // a_out / b_out hold at most rows_capacity rows; the kernel only writes the tiles the mode selects
+        if ((rc = out_map_2d(o, 1, a_out, plan->rows_capacity, H)) != MOMOE_OK) return rc;
+        if ((rc = out_map_2d(o, 2, b_out, plan->rows_capacity, H)) != MOMOE_OK) return rc;
+    }
+    return launch<MODE_UP>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
+}
+
+#define MOMOE_API extern "C" __attribute__((visibility("default")))
+
+MOMOE_API int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted, const void* W1_ND2H, void* h_sorted,
+                              void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream) {
+    return up_swiglu_impl(plan, x_sorted, false, W1_ND2H, h_sorted, a_out, b_out, ab_mode, stream);
+}
+
+MOMOE_API int momoe_up_swiglu_tokens(const momoe_plan_t* plan, const void* x_MD, const void* W1_ND2H, void* h_sorted,
+                                     void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream) {
+    return up_swiglu_impl(plan, x_MD, true, W1_ND2H, h_sorted, a_out, b_out, ab_mode, stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int momoe_down_scale(const momoe_plan_t* plan, const void* h_sorted,
@@ -726,27 +861,29 @@ extern "C" __attribute__((visibility("default"))) int momoe_down_scale(const mom
     g.nkb = cdiv(H, KB);
     g.out_cols = D;
     g.out0 = static_cast<__nv_bfloat16*>(y_sorted);
-    return launch<MODE_DOWN>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
+    OutMaps o;
+    if ((rc = out_map_2d(o, 0, y_sorted, plan->rows_capacity, D)) != MOMOE_OK) return rc;
+    o.m[1] = o.m[2] = o.m[0];
+    return launch<MODE_DOWN>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" __attribute__((visibility("default"))) int momoe_dgrad2_swiglu_bwd(
-    const momoe_plan_t* plan, const void* g_sorted, const void* W2_NHD, const void* a_saved, const void* b_saved,
-    const void* a_recomp, const void* b_recomp, void* gz_sorted, void* hs_sorted, float* gs_part,
-    momoe_stream_t stream) {
+static int dgrad2_impl(const momoe_plan_t* plan, const void* gy, bool tokens, const void* W2_NHD, const void* a_saved,
+                       const void* b_saved, const void* a_recomp, const void* b_recomp, void* gz_sorted,
+                       void* hs_sorted, float* gs_part, momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
-    if (g_sorted == nullptr || W2_NHD == nullptr || gz_sorted == nullptr || hs_sorted == nullptr || gs_part == nullptr)
+    if (gy == nullptr || W2_NHD == nullptr || gz_sorted == nullptr || hs_sorted == nullptr || gs_part == nullptr)
         return MOMOE_ERR_ARG;
     if ((a_saved == nullptr) != (b_saved == nullptr) || (a_recomp == nullptr) != (b_recomp == nullptr))
         return MOMOE_ERR_ARG;
     if (a_saved == nullptr && a_recomp == nullptr) return MOMOE_ERR_ARG;
     const int D = plan->D, H = plan->H;
     CUtensorMap tmA, tmB;
-    if ((rc = encode_tmap_2d(&tmA, g_sorted, plan->rows_capacity, D, TILE_M, TILE_K)) != MOMOE_OK) return rc;
-    // W2[e] is [H, D]: as the B operand its rows are the H output columns and D is the contiguous k axis
-    if ((rc = encode_tmap_3d(&tmB, W2_NHD, plan->N, H, D, 128, TILE_K)) != MOMOE_OK) return rc;
     GemmArgs g;
     base_args(plan, g);
+    if ((rc = a_operand(plan, gy, D, tokens, &tmA, g)) != MOMOE_OK) return rc;
+    // W2[e] is [H, D]: as the B operand its rows are the H output columns and D is the contiguous k axis
+    if ((rc = encode_tmap_3d(&tmB, W2_NHD, plan->N, H, D, 128, TILE_K)) != MOMOE_OK) return rc;
     g.n_nblk = cdiv(H, PAIR_N);
     g.nkb = cdiv(D, KB);
     g.out_cols = H;
@@ -757,7 +894,35 @@ extern "C" __attribute__((visibility("default"))) int momoe_dgrad2_swiglu_bwd(
     g.a_recomp = static_cast<const __nv_bfloat16*>(a_recomp);
     g.b_recomp = static_cast<const __nv_bfloat16*>(b_recomp);
     g.gs_part = gs_part;
-    return launch<MODE_DGRAD2>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
+    OutMaps o;
+    {
+        // gz [rows, 2H] addressed as [rows, 2, H] so that a piece of the linear half is clipped at column H;
+        // pieces of 32 rows x 16 columns (32-byte rows, 32-byte swizzle)
+        const uint64_t dims[3] = {static_cast<uint64_t>(H), 2, static_cast<uint64_t>(plan->rows_capacity)};
+        const uint64_t strides[2] = {static_cast<uint64_t>(H) * 2, static_cast<uint64_t>(H) * 4};
+        const uint32_t box[3] = {16, 1, 32};
+        if ((rc = encode_tmap(&o.m[0], gz_sorted, 3, dims, strides, box, TMAP_SWIZZLE_32B)) != MOMOE_OK) return rc;
+    }
+    if ((rc = encode_tmap_2d(&o.m[1], hs_sorted, plan->rows_capacity, H, 32, 16, TMAP_SWIZZLE_32B)) != MOMOE_OK)
+        return rc;
+    o.m[2] = o.m[1];
+    return launch<MODE_DGRAD2>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
+}
+
+MOMOE_API int momoe_dgrad2_swiglu_bwd(const momoe_plan_t* plan, const void* g_sorted, const void* W2_NHD,
+                                      const void* a_saved, const void* b_saved, const void* a_recomp,
+                                      const void* b_recomp, void* gz_sorted, void* hs_sorted, float* gs_part,
+                                      momoe_stream_t stream) {
+    return dgrad2_impl(plan, g_sorted, false, W2_NHD, a_saved, b_saved, a_recomp, b_recomp, gz_sorted, hs_sorted,
+                       gs_part, stream);
+}
+
+MOMOE_API int momoe_dgrad2_swiglu_bwd_tokens(const momoe_plan_t* plan, const void* g_MD, const void* W2_NHD,
+                                             const void* a_saved, const void* b_saved, const void* a_recomp,
+                                             const void* b_recomp, void* gz_sorted, void* hs_sorted, float* gs_part,
+                                             momoe_stream_t stream) {
+    return dgrad2_impl(plan, g_MD, true, W2_NHD, a_saved, b_saved, a_recomp, b_recomp, gz_sorted, hs_sorted, gs_part,
+                       stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int momoe_dgrad1(const momoe_plan_t* plan, const void* gz_sorted,
@@ -777,26 +942,56 @@ extern "C" __attribute__((visibility("default"))) int momoe_dgrad1(const momoe_p
     g.nkb = cdiv(2 * H, KB);
     g.out_cols = D;
     g.out0 = static_cast<__nv_bfloat16*>(gx_sorted);
-    return launch<MODE_DGRAD1>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
+    OutMaps o;
+    if ((rc = out_map_2d(o, 0, gx_sorted, plan->rows_capacity, D)) != MOMOE_OK) return rc;
+    o.m[1] = o.m[2] = o.m[0];
+    return launch<MODE_DGRAD1>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" __attribute__((visibility("default"))) int momoe_wgrad(const momoe_plan_t* plan, const void* a_sorted,
-                                                                 int32_t X, const void* b_sorted, int32_t Y,
-                                                                 void* dW_NXY, momoe_stream_t stream) {
+static int wgrad_impl(const momoe_plan_t* plan, const void* a, int32_t X, bool a_tokens, const void* b, int32_t Y,
+                      bool b_tokens, void* dW_NXY, momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
-    if (a_sorted == nullptr || b_sorted == nullptr || dW_NXY == nullptr || X <= 0 || Y <= 0) return MOMOE_ERR_ARG;
+    if (a == nullptr || b == nullptr || dW_NXY == nullptr || X <= 0 || Y <= 0) return MOMOE_ERR_ARG;
     if (X % 8 != 0 || Y % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
+    if ((a_tokens || b_tokens) &&
+        (plan->row_token == nullptr || (reinterpret_cast<uintptr_t>(plan->row_token) & 15) != 0))
+        return MOMOE_ERR_ARG;
     CUtensorMap tmA, tmB;
-    // both operands are read as [64 rows (k) x 64 columns (m or n)] boxes: MN-major
-    if ((rc = encode_tmap_2d(&tmA, a_sorted, plan->rows_capacity, X, TILE_K, 64)) != MOMOE_OK) return rc;
-    if ((rc = encode_tmap_2d(&tmB, b_sorted, plan->rows_capacity, Y, TILE_K, 64)) != MOMOE_OK) return rc;
+    // both operands are read as [64 rows (k) x 64 columns (m or n)] boxes: MN-major; a token-major operand is read
+    // four rows at a time ([1 x 64] boxes) through plan->row_token and lands in the same layout
+    if ((rc = a_tokens ? encode_tmap_2d(&tmA, a, plan->M, X, 1, 64)
+                       : encode_tmap_2d(&tmA, a, plan->rows_capacity, X, TILE_K, 64)) != MOMOE_OK)
+        return rc;
+    if ((rc = b_tokens ? encode_tmap_2d(&tmB, b, plan->M, Y, 1, 64)
+                       : encode_tmap_2d(&tmB, b, plan->rows_capacity, Y, TILE_K, 64)) != MOMOE_OK)
+        return rc;
     GemmArgs g;
     base_args(plan, g);
+    if (a_tokens || b_tokens) {
+        g.rows = plan->row_token;
+        g.gather = (a_tokens ? 1 : 0) | (b_tokens ? 2 : 0);
+        g.n_tokens = plan->M;
+    }
     g.n_mblk = cdiv(X, 256);
     g.n_nblk = cdiv(Y, PAIR_N);
     g.out_rows = X;
     g.out_cols = Y;
     g.out0 = static_cast<__nv_bfloat16*>(dW_NXY);
-    return launch<MODE_WGRAD>(tmA, tmB, g, static_cast<cudaStream_t>(stream));
+    OutMaps o;
+    // [N, X, Y] in pieces of 32 rows x 32 columns of one expert: rows past X are clipped, not written into expert e+1
+    if ((rc = encode_tmap_3d(&o.m[0], dW_NXY, plan->N, X, Y, 32, 32, TMAP_SWIZZLE_64B)) != MOMOE_OK) return rc;
+    o.m[1] = o.m[2] = o.m[0];
+    return launch<MODE_WGRAD>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
+}
+
+MOMOE_API int momoe_wgrad(const momoe_plan_t* plan, const void* a_sorted, int32_t X, const void* b_sorted, int32_t Y,
+                          void* dW_NXY, momoe_stream_t stream) {
+    return wgrad_impl(plan, a_sorted, X, false, b_sorted, Y, false, dW_NXY, stream);
+}
+
+MOMOE_API int momoe_wgrad_tokens(const momoe_plan_t* plan, const void* a, int32_t X, int32_t a_is_token_major,
+                                 const void* b, int32_t Y, int32_t b_is_token_major, void* dW_NXY,
+                                 momoe_stream_t stream) {
+    return wgrad_impl(plan, a, X, a_is_token_major != 0, b, Y, b_is_token_major != 0, dW_NXY, stream);
 }

@@ -35,9 +35,14 @@ enum : int {
 enum : int { SCHED_N_TILES = 0, SCHED_N_SAVED_TILES = 1, SCHED_PAD_ROWS = 2, SCHED_N_PAIRS = 3, SCHED_WORDS = 8 };
 
 int sm_count();
+// Shared-memory swizzle of a tensor map: the byte span inside which TMA permutes 16-byte chunks.
+enum TmapSwizzle : int { TMAP_SWIZZLE_128B = 0, TMAP_SWIZZLE_64B = 1, TMAP_SWIZZLE_32B = 2 };
 int encode_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                   uint32_t box_cols);
+                   uint32_t box_cols, int swizzle = TMAP_SWIZZLE_128B);
 int encode_tmap_3d(CUtensorMap* m, const void* base, uint64_t d2, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                   uint32_t box_cols);
+                   uint32_t box_cols, int swizzle = TMAP_SWIZZLE_128B);
+// General form: dims / box innermost first, strides (bytes) of dimensions 1..rank-1.
+int encode_tmap(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                const uint32_t* box, int swizzle);
 
 }  // namespace momoe

@@ -78,6 +78,35 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
         : "memory");
 }
 
+// TMA stores: a box of shared memory, written by this CTA's threads and published to the async proxy with
+// fence_proxy_async_smem(), goes to global memory; parts of the box outside the tensor are not written.  Completion is
+// tracked per issuing thread in bulk groups.  The innermost coordinate times the element size must be a multiple of
+// 16 bytes, and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most N of this thread's most recent bulk groups are still READING their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Until at most N of this thread's most recent bulk groups are still in flight at all.
+template <int N>
+__device__ __forceinline__ void bulk_wait_all() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {  // one full warp
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
@@ -161,6 +190,20 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
     asm volatile(
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// Row-gather load: four rows of a 2-D tensor (row indices r0..r3, all starting at column c0) land as four consecutive
+// 128-byte rows at `dst`.  The tensor map's box is {64 columns, 1 row}; with the 128-byte swizzle the bytes are
+// placed as a tiled load of the same four rows would place them, so a K-major [128 x 64] operand tile is 32 of these
+// (dst advancing by 512 bytes).  One destination CTA; the bytes are credited to the mbarrier at
+// `bar_cluster_addr`, which may live in the pair's leader CTA.  c0 * 2 must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_gather4_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0,
+                                                 int r0, int r1, int r2, int r3) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2 "
+        "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(r0), "r"(r1), "r"(r2),
+          "r"(r3)
         : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {  // same warp id in both CTAs

@@ -46,17 +46,21 @@ _PROTOS = {
     "momoe_gather_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_combine_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_up_swiglu": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
+    "momoe_up_swiglu_tokens": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "momoe_down_scale": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_up_swiglu_decode": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_down_scale_decode": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_dgrad2_swiglu_bwd": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "momoe_dgrad2_swiglu_bwd_tokens": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "momoe_dgrad1": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_wgrad": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp, c_vp]),
+    "momoe_wgrad_tokens": (C.c_int, [PlanP, c_vp, c_i32, c_i32, c_vp, c_i32, c_i32, c_vp, c_vp]),
     "momoe_scatter_gs": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_router_backward": (C.c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_vp,
                                         c_vp]),
     "momoe_router_backward_compact": (C.c_int, [c_vp, c_vp, c_i32, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_vp]),
     "momoe_bias_update": (C.c_int, [c_vp, c_vp, c_i32, c_i32, C.c_float, C.c_float, c_vp]),
+    "momoe_ep_set_wait_limit": (c_i64, [c_i64]),
     "momoe_ep_publish_counts": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_i32, c_i32, c_u32, c_vp, c_vp]),
     "momoe_ep_barrier": (C.c_int, [c_vp, c_i32, c_i32, c_u32, c_vp, c_vp]),
     "momoe_ep_plan": (C.c_int, [c_vp, c_i32, c_i32, c_i32, C.c_double, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,

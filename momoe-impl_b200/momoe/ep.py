@@ -16,12 +16,15 @@ Backward mirrors forward with the upstream gradient.  Payload always lands in th
 grouped GEMMs read it; no TMA load ever addresses a peer.
 """
 import ctypes as C
+import os
+import weakref
 
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
 from . import ops
+from .momoe import _CHECK
 from .topk_router import CompactRouterFunction, TopKRouter
 
 
@@ -190,6 +193,9 @@ class PeerBuffers:
         self.cap_rows = cap_rows
         self.epoch = 0
         self._keep = []
+        self.max_tokens = 0        # tokens per rank the buffers were sized for (set by the layer)
+        self._step = 0             # forward passes started
+        self._pending = 0          # step whose backward pass has not run yet (0: none)
 
         def alloc(shape, dtype):
             t = symm_mem.empty(shape, dtype=dtype, device=device)
@@ -215,6 +221,29 @@ class PeerBuffers:
         self.epoch += 1
         return self.epoch
 
+    # One set of buffers serves one step at a time: `rows_x` / `row_w` written by a forward pass are read again by its
+    # backward pass, and `rows_y` / `rows_g` are reused by both.  A second forward pass before that backward pass
+    # (pipeline micro-batches, activation checkpointing, an evaluation pass in between) would silently overwrite them,
+    # so it is refused instead.
+    def begin_step(self, needs_backward):
+        if self._pending:
+            raise RuntimeError(
+                "ExpertParallelMoE (peer transport): forward called while the backward pass of the previous forward is "
+                "still outstanding; its peer buffers hold one step at a time.  Run the backward pass first, wrap "
+                "passes that need no gradient in torch.no_grad(), drop the previous output, or use transport='nccl'.")
+        self._step += 1
+        if needs_backward:
+            self._pending = self._step
+        return self._step
+
+    def end_step(self, step):
+        if self._pending == step:
+            self._pending = 0
+
+
+class _StepToken:
+    """Lifetime marker of one forward pass's autograd node."""
+
 
 class PeerExpertParallelFunction(torch.autograd.Function):
     """Expert computation with dispatch / combine over peer memory (see the module docstring)."""
@@ -235,6 +264,10 @@ class PeerExpertParallelFunction(torch.autograd.Function):
         x_MD = x_BSD.reshape(M, D).to(device=dev, dtype=torch.bfloat16).contiguous()
         W1 = W1_local.detach().to(torch.bfloat16).contiguous()
         W2 = W2_local.detach().to(torch.bfloat16).contiguous()
+        step = bufs.begin_step(any(ctx.needs_input_grad))
+        ctx.step = step
+        ctx.step_token = _StepToken()      # dies with the autograd graph: an output dropped without backward frees the buffers
+        weakref.finalize(ctx.step_token, bufs.end_step, step)
         with torch.cuda.device(dev):
             home = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, H, 0.0)
             status = home.status
@@ -288,6 +321,9 @@ class PeerExpertParallelFunction(torch.autograd.Function):
         ctx.has_ab = a_save is not None
         ctx.save_for_backward(*([W1, W2] + ([a_save, b_save] if ctx.has_ab else [])))
         ctx.mark_non_differentiable(sizes_global)
+        ops.status_post(dev)
+        if _CHECK:
+            ops.check_status(dev)
         return y_MD.reshape(B, S, D).to(x_BSD.device), sizes_global
 
     @staticmethod
@@ -361,14 +397,42 @@ class PeerExpertParallelFunction(torch.autograd.Function):
             G_W1 = torch.empty_like(W1)
             ops._call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, lp, ptr(bufs.rows_x), D, ptr(gz), 2 * H, ptr(G_W1), st())
             main.wait_event(ev[3])
+        bufs.end_step(ctx.step)
+        ops.status_post(dev)
+        if _CHECK:
+            ops.check_status(dev)
         x_dev, w_dev = ctx.in_devices
         return (G_x.reshape(B, S, D).to(x_dev), G_W1, G_W2, None, G_w.to(w_dev), None, None, None)
 
 
+class _ExpertBlock(nn.Module):
+    """This rank's block of N/R experts.  The layer names it `momoe`, so parameter keys read `momoe.Wl1_ND2H` /
+    `momoe.Wl2_NHD` exactly as in the single-GPU `MoE` (momoe/sample_moe.py:48-55 of the reference)."""
+
+    def __init__(self, Wl1_ND2H, Wl2_NHD):
+        super().__init__()
+        self.Wl1_ND2H = nn.Parameter(Wl1_ND2H.clone().detach().to(torch.bfloat16), requires_grad=True)
+        self.Wl2_NHD = nn.Parameter(Wl2_NHD.clone().detach().to(torch.bfloat16), requires_grad=True)
+
+
 class ExpertParallelMoE(nn.Module):
     """`MoE` with the experts sharded over a process group: same forward signature and bias update; the router is
-    replicated, `Wl1_ND2H` / `Wl2_NHD` hold this rank's block of N/R experts, and `tokens_per_expert_N` (which drives
-    the bias update) is the global count summed over ranks."""
+    replicated, `momoe.Wl1_ND2H` / `momoe.Wl2_NHD` hold this rank's block of N/R experts, and `tokens_per_expert_N`
+    (which drives the bias update) is the global count summed over ranks.
+
+    Checkpoints keep the single-GPU layout and key names (`router.Wg_DN`, `momoe.Wl1_ND2H`, `momoe.Wl2_NHD`,
+    `biases_N`; momoe/sample_moe.py:39-57, momoe/momoe.py:947-955 of the reference): `load_state_dict` accepts a
+    checkpoint of the single-GPU layer (every rank keeps its block of the `[N, ...]` tensors; a checkpoint that already
+    holds `[N/R, ...]` blocks is taken as is), and `state_dict()` returns the `[N, ...]` tensors again by all-gathering
+    the blocks, which makes it a COLLECTIVE call: every rank of the group must make it.  Set
+    `full_checkpoints = False` to save and load the local blocks only.
+
+    Limits of the peer transport (the default): its buffers hold one step at a time, so a second forward pass before
+    the previous one's backward pass raises; and the buffers are (re)allocated collectively, so the call that first
+    needs them, or needs larger ones, must be reached by every rank (same token count per rank, or `reserve()` with
+    the largest count up front).  Device-side problems (status 301: a peer did not reach a hand-shake in time,
+    302: the routing does not fit the buffers, raise `capacity_factor`) are reported as a RuntimeError by the NEXT
+    forward pass without synchronising the host; `MOMOE_B200_CHECK=1` reports them at the end of the same pass."""
 
     def __init__(self, embedding_dim, intermediate_dim, num_experts, num_chosen_experts, num_shared_experts,
                  save_percent=0, bias_update_rate=1e-4, Wg_DN=None, Wl1_ND2H=None, Wl2_NHD=None, *, group=None,
@@ -386,6 +450,7 @@ class ExpertParallelMoE(nn.Module):
         assert transport in ("peer", "nccl")
         self.transport = transport
         self.capacity_factor = capacity_factor
+        self.full_checkpoints = True
         self._bufs = None
         Nl = num_experts // R
         self.router = TopKRouter(embedding_dim, num_experts, num_chosen_experts, num_shared_experts, Wg_DN=Wg_DN)
@@ -395,27 +460,39 @@ class ExpertParallelMoE(nn.Module):
         if Wl2_NHD is None:
             Wl2_NHD = torch.randn((Nl, self.H, self.D), device=dev, dtype=torch.bfloat16) / self.D
         assert Wl1_ND2H.shape[0] == Nl and Wl2_NHD.shape[0] == Nl, "pass this rank's block of N/R experts"
-        self.Wl1_ND2H = nn.Parameter(Wl1_ND2H.clone().detach().to(torch.bfloat16), requires_grad=True)
-        self.Wl2_NHD = nn.Parameter(Wl2_NHD.clone().detach().to(torch.bfloat16), requires_grad=True)
+        self.momoe = _ExpertBlock(Wl1_ND2H, Wl2_NHD)
         self.biases_N = nn.Parameter(
             torch.cat([torch.zeros(self.N - self.Ks, device=dev, dtype=torch.float32),
                        torch.full((self.Ks,), float("-inf"), device=dev, dtype=torch.float32)], dim=-1),
             requires_grad=False)
+        self._register_load_state_dict_pre_hook(self._shard_checkpoint)
+        self._register_state_dict_hook(ExpertParallelMoE._gather_checkpoint)
+
+    # this rank's expert block under the names the single-GPU layer's users know
+    @property
+    def Wl1_ND2H(self):
+        return self.momoe.Wl1_ND2H
+
+    @property
+    def Wl2_NHD(self):
+        return self.momoe.Wl2_NHD
 
     def forward(self, x_BSD):
         B, S, _ = x_BSD.shape
+        ops.status_poll(self.momoe.Wl1_ND2H.device)    # raises if an earlier pass left a device-side error code
         if self.transport == "peer":
             # compact routing end to end: ids and weights [M,K]; the weights carry the gradient back to the router
             topk_idx, topk_w = CompactRouterFunction.apply(x_BSD, self.router.Wg_DN, self.biases_N, self.N, self.K,
                                                            self.Ks)
             bufs = self._peer_buffers(B * S)
-            y_BSD, sizes_N = PeerExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, topk_idx, topk_w,
-                                                              self.K, self.save_percent, bufs)
+            y_BSD, sizes_N = PeerExpertParallelFunction.apply(x_BSD, self.momoe.Wl1_ND2H, self.momoe.Wl2_NHD,
+                                                              topk_idx, topk_w, self.K, self.save_percent, bufs)
         else:
             x_BSD, mask_NM, s_NM = self.router(x_BSD, self.biases_N)
-            topk_idx, topk_w = mask_NM._momoe_topk
-            y_BSD, sizes_N = ExpertParallelFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM, topk_idx,
-                                                          topk_w, self.K, self.save_percent, self.group)
+            topk_idx, topk_w = mask_NM._momoe_topk[:2]
+            y_BSD, sizes_N = ExpertParallelFunction.apply(x_BSD, self.momoe.Wl1_ND2H, self.momoe.Wl2_NHD, mask_NM,
+                                                          s_NM, topk_idx, topk_w, self.K, self.save_percent,
+                                                          self.group)
         R = dist.get_world_size(self.group)
         c_avg = B * S * R * (self.K - self.Ks) / (self.N - self.Ks)
         with torch.no_grad():
@@ -423,39 +500,76 @@ class ExpertParallelMoE(nn.Module):
         return y_BSD
 
     # ---- checkpoints in the single-GPU layout (keys router.Wg_DN, momoe.Wl1_ND2H, momoe.Wl2_NHD, biases_N)
-    def load_full_state_dict(self, state):
-        """Load a checkpoint of the single-GPU `MoE` layer: every rank keeps its own block of experts."""
+    def _block(self, full):
         R, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         Nl = self.N // R
-        with torch.no_grad():
-            self.router.Wg_DN.copy_(state["router.Wg_DN"])
-            self.biases_N.copy_(state["biases_N"])
-            self.Wl1_ND2H.copy_(state["momoe.Wl1_ND2H"][rank * Nl:(rank + 1) * Nl])
-            self.Wl2_NHD.copy_(state["momoe.Wl2_NHD"][rank * Nl:(rank + 1) * Nl])
+        return full[rank * Nl:(rank + 1) * Nl]
+
+    def _shard_checkpoint(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        """load_state_dict pre-hook: an `[N, ...]` expert tensor of a single-GPU checkpoint is cut down to this rank's
+        block (the dict handed to the hook is load_state_dict's own copy)."""
+        for name in ("momoe.Wl1_ND2H", "momoe.Wl2_NHD"):
+            key = prefix + name
+            t = state_dict.get(key)
+            if t is not None and t.dim() == 3 and t.shape[0] == self.N and self.N != self.momoe.Wl1_ND2H.shape[0]:
+                state_dict[key] = self._block(t)
+
+    @staticmethod
+    def _gather_checkpoint(module, state_dict, prefix, local_metadata):
+        """state_dict hook: the expert blocks are all-gathered into the single-GPU `[N, ...]` tensors (collective)."""
+        if not module.full_checkpoints or dist.get_world_size(module.group) == 1:
+            return
+        for name in ("momoe.Wl1_ND2H", "momoe.Wl2_NHD"):
+            key = prefix + name
+            if key in state_dict:
+                state_dict[key] = module._all_gather_blocks(state_dict[key])
+
+    def _all_gather_blocks(self, w):
+        R = dist.get_world_size(self.group)
+        w = w.detach().contiguous()
+        out = torch.empty((R,) + tuple(w.shape), dtype=w.dtype, device=w.device)
+        # raw bytes: every backend moves uint8
+        dist.all_gather_into_tensor(out.view(torch.uint8).reshape(-1), w.view(torch.uint8).reshape(-1),
+                                    group=self.group)
+        return out.reshape((R * w.shape[0],) + tuple(w.shape[1:]))
+
+    def load_full_state_dict(self, state):
+        """Load a checkpoint of the single-GPU `MoE` layer: every rank keeps its own block of experts.  Same as
+        `load_state_dict(state)`; kept for callers of the explicit name."""
+        return self.load_state_dict(state)
 
     def full_state_dict(self):
-        """The layer's parameters in the single-GPU layout, on every rank (expert blocks are all-gathered)."""
-        R = dist.get_world_size(self.group)
+        """The layer's parameters in the single-GPU layout, on every rank (expert blocks are all-gathered; collective).
+        Same as `state_dict()` with `full_checkpoints` set."""
+        keep, self.full_checkpoints = self.full_checkpoints, True
+        try:
+            return {k: v.detach().clone() for k, v in self.state_dict().items()}
+        finally:
+            self.full_checkpoints = keep
 
-        def gather(w):
-            w = w.detach().contiguous()
-            out = torch.empty((R,) + tuple(w.shape), dtype=w.dtype, device=w.device)
-            # raw bytes: every backend moves uint8
-            dist.all_gather_into_tensor(out.view(torch.uint8).reshape(-1), w.view(torch.uint8).reshape(-1),
-                                        group=self.group)
-            return out.reshape((R * w.shape[0],) + tuple(w.shape[1:]))
-
-        return {"router.Wg_DN": self.router.Wg_DN.detach().clone(), "biases_N": self.biases_N.detach().clone(),
-                "momoe.Wl1_ND2H": gather(self.Wl1_ND2H), "momoe.Wl2_NHD": gather(self.Wl2_NHD)}
-
-    def _peer_buffers(self, M):
-        """Symmetric buffers sized for `capacity_factor` times the average number of rows a rank receives (plus one
-        partial tile per local expert); allocated collectively on first use and whenever more tokens arrive."""
+    # ---- peer buffers
+    def _rows_for(self, M):
         R = dist.get_world_size(self.group)
         Nl = self.N // R
         # routed experts: capacity_factor x the balanced share; shared experts receive every token of every rank
         want = int(M * (self.K - self.Ks) * self.capacity_factor) + R * M * self.Ks + Nl * 128
-        want = (want + 127) // 128 * 128
-        if self._bufs is None or self._bufs.cap_rows < want:
-            self._bufs = PeerBuffers(self.group, self.Wl1_ND2H.device, self.N, self.D, want)
+        return (want + 127) // 128 * 128
+
+    def reserve(self, max_tokens_per_rank):
+        """Allocate the peer buffers for up to `max_tokens_per_rank` tokens on every rank.  COLLECTIVE: every rank of
+        the group must call it, with the same value.  Call it up front when ranks will see different token counts."""
+        self._bufs = PeerBuffers(self.group, self.momoe.Wl1_ND2H.device, self.N, self.D,
+                                 self._rows_for(max_tokens_per_rank))
+        self._bufs.max_tokens = max_tokens_per_rank
+        return self._bufs
+
+    def _peer_buffers(self, M):
+        """Symmetric buffers sized for `capacity_factor` times the average number of rows a rank receives (plus one
+        partial tile per local expert).  They are allocated collectively on first use and whenever a rank brings more
+        tokens than they were sized for; that call agrees on the largest token count of the group first (one small
+        all-reduce and a host read, on that call only), so every rank must reach it."""
+        if self._bufs is None or M > self._bufs.max_tokens:
+            m = torch.tensor([M], dtype=torch.int64, device=self.momoe.Wl1_ND2H.device)
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
+            self.reserve(int(m.item()))
         return self._bufs

@@ -15,6 +15,27 @@ from ._lib import require_cuda
 _CHECK = os.environ.get("MOMOE_B200_CHECK", "0") == "1"
 
 
+def attach_compact_routing(mask_NM, s_NM, topk_idx, topk_w):
+    """Let the dense router outputs carry the compact form of the same routing (ids and weights [M,K]), so that
+    `MoMoE` need not re-derive it from the mask.  The tag records both tensors' version counters."""
+    tag = (topk_idx, topk_w, mask_NM._version, s_NM._version)
+    mask_NM._momoe_topk = tag
+    s_NM._momoe_topk = tag
+
+
+def compact_routing_of(mask_NM, s_NM):
+    """The compact routing attached by `TopKRouter`, or None.  It is only trusted when BOTH tensors passed in are
+    the very objects the router returned and neither has been written since: a caller that rescales `s_NM`, passes
+    other weights, or edits `mask_NM` in place (the reference reads whatever it is given, momoe/momoe.py:235-237,
+    760-815) gets the routing re-derived from the dense tensors."""
+    tag = getattr(mask_NM, "_momoe_topk", None)
+    if tag is None or getattr(s_NM, "_momoe_topk", None) is not tag:
+        return None
+    if mask_NM._version != tag[2] or s_NM._version != tag[3]:
+        return None
+    return tag[0], tag[1]
+
+
 class MoEFunction(torch.autograd.Function):
     """Forward / backward orchestration; stands in for momoe/momoe.py:847-903 of the reference."""
 
@@ -31,7 +52,7 @@ class MoEFunction(torch.autograd.Function):
         W1 = Wl1_ND2H.detach().to(torch.bfloat16).contiguous()
         W2 = Wl2_NHD.detach().to(torch.bfloat16).contiguous()
         with torch.cuda.device(dev):
-            compact = getattr(mask_NM, "_momoe_topk", None)
+            compact = compact_routing_of(mask_NM, s_NM)
             if compact is not None and compact[0].shape == (B * S, K):
                 plan = ops.RoutingPlan.from_topk(compact[0], compact[1], N, D, H, save_percent)
             else:
@@ -47,6 +68,7 @@ class MoEFunction(torch.autograd.Function):
             saved += [a_save, b_save]
         ctx.save_for_backward(*saved)
         ctx.mark_non_differentiable(plan.sizes)
+        ops.status_post(dev)
         if _CHECK:
             ops.check_status(dev)
         return y_MD.reshape(B, S, D).to(device=x_BSD.device), plan.sizes
@@ -62,6 +84,7 @@ class MoEFunction(torch.autograd.Function):
         g_MD = G_y_BSD.reshape(B * S, D).to(device=dev, dtype=torch.bfloat16).contiguous()
         with torch.cuda.device(dev):
             G_x, G_W1, G_W2, G_s = ops.experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save)
+        ops.status_post(dev)
         if _CHECK:
             ops.check_status(dev)
         x_dev, s_dev = ctx.in_devices
@@ -106,6 +129,7 @@ class MoMoE(nn.Module):
     def forward(self, x_BSD, mask_NM, s_NM):
         """x_BSD [B,S,D]; mask_NM int32 [N,M] of 0/1 with exactly K ones per token; s_NM [N,M] routing weights
         (zero where unselected).  Returns (y_BSD bf16, tokens_per_expert_N int64)."""
+        ops.status_poll(self.Wl1_ND2H.device)      # raises if an earlier pass left a device-side error code
         y_BSD, sizes_N = MoEFunction.apply(x_BSD, self.Wl1_ND2H, self.Wl2_NHD, mask_NM, s_NM, self.K,
                                            self.save_percent)
         return y_BSD, sizes_N

@@ -58,7 +58,57 @@ def check_status(device=None):
     v = int(w.item())
     if v != 0:
         w.zero_()
+        rep = _status_reports.get(w.device.index)
+        if rep is not None:      # a copy of the same code may be on its way to the host: it has been reported now
+            torch.cuda.synchronize(w.device)
+            rep["posted"] = False
+            rep["host"][0] = 0
         raise RuntimeError("momoe device status %d: %s" % (v, _STATUS_TEXT.get(v, "unknown")))
+
+
+# Asynchronous report of the status word: at the end of a pass the word is copied to pinned host memory with a
+# non-blocking copy; the next pass looks at the copy once the copy's event has completed and raises if a kernel left a
+# code there.  The host is never synchronised, so an error surfaces one pass late (MOMOE_B200_CHECK=1 reports it at
+# the end of the same pass, with a synchronisation).  MOMOE_B200_ASYNC_STATUS=0 switches the report off (the word can
+# still be read with check_status); it is also skipped while a CUDA graph is being captured.
+ASYNC_STATUS = os.environ.get("MOMOE_B200_ASYNC_STATUS", "1") == "1"
+_status_reports = {}
+
+
+def status_post(device):
+    """Queue a copy of the device's status word to pinned host memory (no host synchronisation)."""
+    if not ASYNC_STATUS or torch.cuda.is_current_stream_capturing():
+        return
+    w = status_word(device)
+    key = w.device.index
+    rep = _status_reports.get(key)
+    if rep is None:
+        rep = _status_reports[key] = dict(host=torch.zeros(1, dtype=torch.int32).pin_memory(),
+                                          event=torch.cuda.Event(), posted=False)
+    elif rep["posted"] and not rep["event"].query():
+        return          # the previous report is still on its way; it will carry any code that is set by then or later
+    rep["host"].copy_(w, non_blocking=True)
+    rep["event"].record(torch.cuda.current_stream(w.device))
+    rep["posted"] = True
+
+
+def status_poll(device):
+    """Raise if a report posted by an earlier pass has arrived with a device-side error code.  Never blocks."""
+    d = torch.device(device)
+    if not ASYNC_STATUS or d.type != "cuda" or not _status_reports:
+        return
+    if torch.cuda.is_current_stream_capturing():
+        return
+    key = d.index if d.index is not None else torch.cuda.current_device()
+    rep = _status_reports.get(key)
+    if rep is None or not rep["posted"] or not rep["event"].query():
+        return
+    rep["posted"] = False
+    v = int(rep["host"][0])
+    if v != 0:
+        rep["host"][0] = 0
+        status_word(device).zero_()
+        raise RuntimeError("momoe device status %d (reported by an earlier pass): %s" % (v, _STATUS_TEXT.get(v, "unknown")))
 
 
 def save_rows(Msum, save_percent):
@@ -176,6 +226,11 @@ def combine_rows(plan, src_sorted, cols):
     return dst
 
 
+# Row gathers folded into the grouped GEMMs (TMA row-gather loads of the token-major x and upstream gradient driven by
+# the plan's row table): no expert-major copy of either is written or read.  MOMOE_B200_FUSED_GATHER=0 restores the
+# separate `momoe_gather_rows` launches in front of the GEMMs.
+FUSED_GATHER = os.environ.get("MOMOE_B200_FUSED_GATHER", "1") == "1"
+
 # Forward-only calls with at most this many rows per expert on average take the weight-streaming kernels
 # (momoe_up_swiglu_decode / momoe_down_scale_decode) instead of the 256-row tile kernels.
 DECODE_MAX_AVG_ROWS = int(os.environ.get("MOMOE_B200_DECODE_ROWS", "16"))
@@ -188,13 +243,12 @@ def experts_forward(plan, x_MD, W1, W2, inference=False):
     dev = x_MD.device
     D, H = plan.D, plan.H
     bf = dict(dtype=torch.bfloat16, device=dev)
-    x_sorted = gather_rows(plan, x_MD, D)
     h = torch.empty((plan.rows_capacity, H), **bf)
+    y_sorted = torch.empty((plan.rows_capacity, D), **bf)
     if inference and plan.Msum <= DECODE_MAX_AVG_ROWS * plan.N:
+        x_sorted = gather_rows(plan, x_MD, D)
         _call("momoe_up_swiglu_decode", 1, lib.momoe_up_swiglu_decode, plan.ref, ptr(x_sorted), ptr(W1), ptr(h),
               stream_ptr())
-        del x_sorted
-        y_sorted = torch.empty((plan.rows_capacity, D), **bf)
         _call("momoe_down_scale_decode", 1, lib.momoe_down_scale_decode, plan.ref, ptr(h), ptr(W2), ptr(y_sorted),
               stream_ptr())
         return combine_rows(plan, y_sorted, D), None, None
@@ -204,13 +258,16 @@ def experts_forward(plan, x_MD, W1, W2, inference=False):
         a_save = torch.empty((plan.saved_tile_capacity * TILE_M, H), **bf)
         b_save = torch.empty((plan.saved_tile_capacity * TILE_M, H), **bf)
         mode = 1
-    _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), ptr(h), ptr(a_save), ptr(b_save), mode,
-                              stream_ptr())
-    del x_sorted
-    y_sorted = torch.empty((plan.rows_capacity, D), **bf)
+    if FUSED_GATHER:
+        _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu_tokens, plan.ref, ptr(x_MD), ptr(W1), ptr(h), ptr(a_save),
+              ptr(b_save), mode, stream_ptr())
+    else:
+        x_sorted = gather_rows(plan, x_MD, D)
+        _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), ptr(h), ptr(a_save),
+              ptr(b_save), mode, stream_ptr())
+        del x_sorted
     _call("momoe_down_scale", 1, lib.momoe_down_scale, plan.ref, ptr(h), ptr(W2), ptr(y_sorted), stream_ptr())
-    y = combine_rows(plan, y_sorted, D)
-    return y, a_save, b_save
+    return combine_rows(plan, y_sorted, D), a_save, b_save
 
 
 def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=True):
@@ -218,25 +275,40 @@ def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=Tru
     dev = x_MD.device
     D, H, N = plan.D, plan.H, plan.N
     bf = dict(dtype=torch.bfloat16, device=dev)
-    g_sorted = gather_rows(plan, g_MD, D)
-    x_sorted = gather_rows(plan, x_MD, D)
+    fused = FUSED_GATHER
+    if fused:
+        g_src, x_src = g_MD, x_MD            # token-major: the GEMMs fetch rows through the plan's row table
+        up, dgrad2 = lib.momoe_up_swiglu_tokens, lib.momoe_dgrad2_swiglu_bwd_tokens
+    else:
+        g_src = gather_rows(plan, g_MD, D)
+        x_src = gather_rows(plan, x_MD, D)
+        up, dgrad2 = lib.momoe_up_swiglu, lib.momoe_dgrad2_swiglu_bwd
     a_rec = b_rec = None
     if plan.recomp_tile_capacity > 0:
         a_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
         b_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
-        _call("momoe_up_swiglu (recompute)", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2, stream_ptr())
+        _call("momoe_up_swiglu (recompute)", 1, up, plan.ref, ptr(x_src), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2,
+              stream_ptr())
     n_part = 2 * ((H + 255) // 256)   # two partial sums per 256-column block (momoe_dgrad2_swiglu_bwd)
     gz = torch.empty((plan.rows_capacity, 2 * H), **bf)
     hs = torch.empty((plan.rows_capacity, H), **bf)
     gs_part = torch.empty((plan.rows_capacity, n_part), dtype=torch.float32, device=dev)
-    _call("momoe_dgrad2_swiglu_bwd", 1, lib.momoe_dgrad2_swiglu_bwd, plan.ref, ptr(g_sorted), ptr(W2), ptr(a_save), ptr(b_save), ptr(a_rec),
-                                      ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), stream_ptr())
+    _call("momoe_dgrad2_swiglu_bwd", 1, dgrad2, plan.ref, ptr(g_src), ptr(W2), ptr(a_save), ptr(b_save), ptr(a_rec),
+          ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), stream_ptr())
     del a_rec, b_rec
     G_W2 = torch.empty_like(W2)
-    _call("momoe_wgrad (W2)", 1, lib.momoe_wgrad, plan.ref, ptr(hs), H, ptr(g_sorted), D, ptr(G_W2), stream_ptr())
     G_W1 = torch.empty_like(W1)
-    _call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, plan.ref, ptr(x_sorted), D, ptr(gz), 2 * H, ptr(G_W1), stream_ptr())
-    gx_sorted = g_sorted  # the gathered upstream gradient is dead after the W2 gradient; reuse its buffer
+    if fused:
+        _call("momoe_wgrad (W2)", 1, lib.momoe_wgrad_tokens, plan.ref, ptr(hs), H, 0, ptr(g_src), D, 1, ptr(G_W2),
+              stream_ptr())
+        _call("momoe_wgrad (W1)", 1, lib.momoe_wgrad_tokens, plan.ref, ptr(x_src), D, 1, ptr(gz), 2 * H, 0, ptr(G_W1),
+              stream_ptr())
+        del hs
+        gx_sorted = torch.empty((plan.rows_capacity, D), **bf)
+    else:
+        _call("momoe_wgrad (W2)", 1, lib.momoe_wgrad, plan.ref, ptr(hs), H, ptr(g_src), D, ptr(G_W2), stream_ptr())
+        _call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, plan.ref, ptr(x_src), D, ptr(gz), 2 * H, ptr(G_W1), stream_ptr())
+        gx_sorted = g_src  # the gathered upstream gradient is dead after the W2 gradient; reuse its buffer
     _call("momoe_dgrad1", 1, lib.momoe_dgrad1, plan.ref, ptr(gz), ptr(W1), ptr(gx_sorted), stream_ptr())
     G_x = combine_rows(plan, gx_sorted, D)
     if need_gs_dense:

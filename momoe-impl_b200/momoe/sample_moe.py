@@ -48,6 +48,7 @@ class FusedMoEFunction(torch.autograd.Function):
             saved += [a_save, b_save]
         ctx.save_for_backward(*saved)
         ctx.mark_non_differentiable(plan.sizes)
+        ops.status_post(dev)
         if _CHECK:
             ops.check_status(dev)
         return y_MD.reshape(B, S, D).to(device=x_BSD.device), plan.sizes
@@ -67,6 +68,7 @@ class FusedMoEFunction(torch.autograd.Function):
             G_L = ops.router_backward_compact(plan, gs_part, Ng_M, Ks_M, ctx.Ks)
             G_x = torch.addmm(G_x, G_L, Wg.T)
             G_Wg = x_MD.T @ G_L
+        ops.status_post(dev)
         if _CHECK:
             ops.check_status(dev)
         return G_x.reshape(B, S, D).to(ctx.x_device), G_Wg, G_W1, G_W2, None, None, None, None
@@ -98,6 +100,7 @@ class MoE(nn.Module):
 
     def forward(self, x_BSD):
         if self.fused:
+            ops.status_poll(self.momoe.Wl1_ND2H.device)  # raises if an earlier pass left a device-side error code
             y_BSD, sizes_N = FusedMoEFunction.apply(x_BSD, self.router.Wg_DN, self.momoe.Wl1_ND2H,
                                                     self.momoe.Wl2_NHD, self.biases_N, self.K, self.Ks,
                                                     self.save_percent)

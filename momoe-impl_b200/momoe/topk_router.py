@@ -90,5 +90,6 @@ class TopKRouter(nn.Module):
         x_BSD, mask_NM, s_NM, topk_idx, topk_w = TopKRouterFunction.apply(x_BSD, self.Wg_DN, biases_N, self.N,
                                                                           self.K, self.Ks)
         # the compact form of the same routing rides along so that MoMoE need not re-derive it from the mask
-        mask_NM._momoe_topk = (topk_idx, topk_w)
+        from .momoe import attach_compact_routing
+        attach_compact_routing(mask_NM, s_NM, topk_idx, topk_w)
         return x_BSD, mask_NM, s_NM

@@ -245,15 +245,18 @@ def bias_update(biases_N, sizes_N, M, K, Ks, rate):
 
 
 def moe_forward_backward(x_BSD, Wg_DN, W1_ND2H, W2_NHD, biases_N, K, Ks, save_percent=0.0,
-                         G_y_BSD=None, loss="sumsq", block_rows=128):
+                         G_y_BSD=None, loss="sumsq", block_rows=128, logits=None):
     """Whole layer as momoe/sample_moe.py:59-68 composes it, followed by the backward of
     `loss = sum(y.float()**2)` (or an explicit upstream gradient).  Returns a dict of every
-    observable tensor."""
+    observable tensor.  `logits` (bf16 [M,N]) replaces the gate GEMM's output (momoe/topk_router.py:95):
+    a caller that compares against a device run passes the logits the device's library GEMM produced, whose
+    bf16 rounding may differ from the CPU GEMM's in the last bit."""
     B, S, D = x_BSD.shape
     M = B * S
     N = W2_NHD.shape[0]
     x_MD = x_BSD.reshape(M, D)
-    logits = gate_logits(x_MD, Wg_DN)
+    if logits is None:
+        logits = gate_logits(x_MD, Wg_DN)
     r = router_from_logits(logits, biases_N, K, Ks)
     sizes, cumsums, idx, which = permutation_from_mask(r["mask_NM"].numpy(), K)
     s_NM = r["s_MN"].T

@@ -92,19 +92,43 @@ def _ckpt_worker(rank, world, port):
     Nl = N // world
     moe = ep.ExpertParallelMoE(D, H, N, K, Ks, Wg_DN=torch.zeros(D, N), Wl1_ND2H=torch.zeros(Nl, D, 2 * H),
                                Wl2_NHD=torch.zeros(Nl, H, D), transport="nccl")
-    moe.load_full_state_dict(full)
+    # the sharded layer exposes the single-GPU layer's keys ...
+    assert sorted(k for k, _ in moe.named_parameters()) == sorted(full)
+    # ... and a plain load_state_dict of a single-GPU checkpoint keeps this rank's expert block (strict: no missing or
+    # unexpected keys, no shape errors)
+    res = moe.load_state_dict(full)
+    assert not res.missing_keys and not res.unexpected_keys
     assert torch.equal(moe.Wl1_ND2H, full["momoe.Wl1_ND2H"][rank * Nl:(rank + 1) * Nl])
     assert torch.equal(moe.Wl2_NHD, full["momoe.Wl2_NHD"][rank * Nl:(rank + 1) * Nl])
-    back = moe.full_state_dict()
+    assert torch.equal(moe.router.Wg_DN, full["router.Wg_DN"]) and torch.equal(moe.biases_N, full["biases_N"])
+    assert full["momoe.Wl1_ND2H"].shape[0] == N                    # the caller's dict is left as it was
+    # state_dict() gives the single-GPU layout back, bit for bit (collective all-gather of the blocks)
+    back = moe.state_dict()
     assert sorted(back) == sorted(full)
     for k in full:
         assert torch.equal(back[k], full[k]), k
+    # the explicit helpers are the same thing
+    moe2 = ep.ExpertParallelMoE(D, H, N, K, Ks, Wg_DN=torch.zeros(D, N), Wl1_ND2H=torch.zeros(Nl, D, 2 * H),
+                                Wl2_NHD=torch.zeros(Nl, H, D), transport="nccl")
+    moe2.load_full_state_dict(full)
+    for k, v in moe2.full_state_dict().items():
+        assert torch.equal(v, full[k]), k
+    # local-block checkpoints: saved without the gather, loaded as they are
+    moe.full_checkpoints = False
+    local = moe.state_dict()
+    assert tuple(local["momoe.Wl1_ND2H"].shape) == (Nl, D, 2 * H)
+    moe2.load_state_dict({k: torch.zeros_like(v) if k.startswith("momoe.") else v for k, v in local.items()})
+    assert float(moe2.Wl1_ND2H.float().abs().sum()) == 0.0
+    moe2.load_state_dict(local)
+    assert torch.equal(moe2.Wl1_ND2H, moe.Wl1_ND2H) and torch.equal(moe2.Wl2_NHD, moe.Wl2_NHD)
     dist.barrier()
     dist.destroy_process_group()
 
 
 def test_checkpoint_round_trip_in_single_gpu_layout():
-    """A single-GPU checkpoint loads into the sharded layer and comes back bit-identical (2 and 3 CPU ranks)."""
+    """A checkpoint of the single-GPU layer (the reference's keys: momoe/sample_moe.py:39-57, momoe/momoe.py:947-955)
+    loads into the sharded layer with a plain `load_state_dict` and `state_dict()` returns it bit-identical (2 and 3 CPU
+    ranks)."""
     mp.spawn(_ckpt_worker, args=(2, _free_port()), nprocs=2, join=True)
     mp.spawn(_ckpt_worker, args=(3, _free_port()), nprocs=3, join=True)
 

@@ -230,3 +230,75 @@ def test_backward_gemms(ops, M, N, K, D, H, skew, save_percent):
     for e in range(N):
         if sizes[e] == 0:   # experts without tokens get exact zeros
             assert float(dW1[e].float().abs().sum()) == 0.0 and float(dW2[e].float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K,D,H,skew", SHAPES + [(4096, 32, 8, 2048, 1024, 1.0)])
+@pytest.mark.parametrize("save_percent", [0, 50])
+def test_token_major_entry_points_match_expert_major(ops, M, N, K, D, H, skew, save_percent):
+    """The entry points that fetch rows of the token-major x / upstream gradient inside the GEMM (TMA row-gather loads
+    through plan->row_token) against the same GEMMs fed with `momoe_gather_rows` copies: every real row and every
+    weight gradient identical bit for bit (same operands, same MMA order; padding rows only ever meet zeros)."""
+    _lib = lib_of(ops)
+    L = _lib.lib
+    ptr, st = _lib.ptr, _lib.stream_ptr
+    plan, x, W1, W2, pad = _setup(ops, M, N, K, D, H, skew, save_percent)
+    rows = pad[-1]
+    bf = dict(dtype=torch.bfloat16, device="cuda")
+    gy = torch.randn(M, D, generator=torch.Generator().manual_seed(9)).bfloat16().cuda()
+    xs = ops.gather_rows(plan, x, D)
+    gs = ops.gather_rows(plan, gy, D)
+    real = plan.row_token[:rows] >= 0
+    nan = float("nan")
+    n_part = 2 * ((H + 255) // 256)
+    mode = 1 if plan.saved_tile_capacity > 0 else 0
+    out = {}
+    for tokens in (False, True):
+        h = torch.full((plan.rows_capacity, H), nan, **bf)
+        a_s = b_s = None
+        if mode:
+            a_s = torch.full((plan.saved_tile_capacity * 128, H), nan, **bf)
+            b_s = torch.full((plan.saved_tile_capacity * 128, H), nan, **bf)
+        a_r = torch.full((plan.recomp_tile_capacity * 128, H), nan, **bf)
+        b_r = torch.full((plan.recomp_tile_capacity * 128, H), nan, **bf)
+        gz = torch.full((plan.rows_capacity, 2 * H), nan, **bf)
+        hs = torch.full((plan.rows_capacity, H), nan, **bf)
+        gsp = torch.full((plan.rows_capacity, n_part), nan, dtype=torch.float32, device="cuda")
+        dW2 = torch.full_like(W2, nan)
+        dW1 = torch.full_like(W1, nan)
+        if tokens:
+            _lib.check(L.momoe_up_swiglu_tokens(plan.ref, ptr(x), ptr(W1), ptr(h), ptr(a_s), ptr(b_s), mode, st()), "up")
+            _lib.check(L.momoe_up_swiglu_tokens(plan.ref, ptr(x), ptr(W1), None, ptr(a_r), ptr(b_r), 2, st()), "up rec")
+            _lib.check(L.momoe_dgrad2_swiglu_bwd_tokens(plan.ref, ptr(gy), ptr(W2), ptr(a_s), ptr(b_s), ptr(a_r),
+                                                        ptr(b_r), ptr(gz), ptr(hs), ptr(gsp), st()), "dgrad2")
+            _lib.check(L.momoe_wgrad_tokens(plan.ref, ptr(hs), H, 0, ptr(gy), D, 1, ptr(dW2), st()), "wgrad2")
+            _lib.check(L.momoe_wgrad_tokens(plan.ref, ptr(x), D, 1, ptr(gz), 2 * H, 0, ptr(dW1), st()), "wgrad1")
+        else:
+            _lib.check(L.momoe_up_swiglu(plan.ref, ptr(xs), ptr(W1), ptr(h), ptr(a_s), ptr(b_s), mode, st()), "up")
+            _lib.check(L.momoe_up_swiglu(plan.ref, ptr(xs), ptr(W1), None, ptr(a_r), ptr(b_r), 2, st()), "up rec")
+            _lib.check(L.momoe_dgrad2_swiglu_bwd(plan.ref, ptr(gs), ptr(W2), ptr(a_s), ptr(b_s), ptr(a_r), ptr(b_r),
+                                                 ptr(gz), ptr(hs), ptr(gsp), st()), "dgrad2")
+            _lib.check(L.momoe_wgrad(plan.ref, ptr(hs), H, ptr(gs), D, ptr(dW2), st()), "wgrad2")
+            _lib.check(L.momoe_wgrad(plan.ref, ptr(xs), D, ptr(gz), 2 * H, ptr(dW1), st()), "wgrad1")
+        torch.cuda.synchronize()
+        ops.check_status()
+        out[tokens] = dict(h=h[:rows][real], gz=gz[:rows], hs=hs[:rows], gs=gsp[:rows][real], dW1=dW1, dW2=dW2)
+    for key in ("h", "gz", "hs", "gs", "dW1", "dW2"):
+        a, b = out[False][key], out[True][key]
+        assert torch.isfinite(b.float()).all(), key
+        assert torch.equal(a, b), "%s differs: max-rel %g" % (key, max_rel(b.float(), a.float()))
+    # gz and hs of padding rows are zero in both forms (zero routing weight)
+    assert float(out[True]["gz"][~real].float().abs().sum()) == 0.0
+    assert float(out[True]["hs"][~real].float().abs().sum()) == 0.0
+    # and the layer through the public sequences, both settings of the switch
+    res = {}
+    for fused in (True, False):
+        ops.FUSED_GATHER = fused
+        try:
+            y, a_save, b_save = ops.experts_forward(plan, x, W1, W2)
+            res[fused] = (y,) + tuple(ops.experts_backward(plan, gy, x, W1, W2, a_save, b_save, need_gs_dense=True))
+        finally:
+            ops.FUSED_GATHER = True
+    torch.cuda.synchronize()
+    ops.check_status()
+    for a, b in zip(res[True], res[False]):
+        assert torch.equal(a, b)

@@ -111,14 +111,10 @@ def test_moe_wrapper_against_oracle(momoe, B, S, D, H, N, K, Ks, sp, bias_std, f
     y = moe(xg)
     (y.float() ** 2).sum().backward()
     _check_status()
-    # oracle with the logits the device produced (the gate GEMM is a library call on both sides)
-    o = orc.moe_forward_backward(x, Wg, W1, W2, biases0, K, Ks, save_percent=sp)
+    # The gate GEMM is a library call on both sides and may round a logit differently; the oracle always routes on
+    # the logits the device produced, so every case is checked whatever the rounding.
     logits_dev = (xg.detach().reshape(B * S, D).bfloat16() @ Wg.to(dev)).cpu()
-    if not torch.equal(logits_dev, o["logits"]):
-        # cuBLAS and the CPU GEMM may round a logit differently; redo the oracle's routing on the device logits
-        r = orc.router_from_logits(logits_dev, biases0, K, Ks)
-        if not torch.equal(r["mask_NM"], o["mask_NM"]):
-            pytest.skip("gate GEMM rounding changes the selection on this input; covered by the fixture tests")
+    o = orc.moe_forward_backward(x, Wg, W1, W2, biases0, K, Ks, save_percent=sp, logits=logits_dev)
     sizes = torch.as_tensor(o["sizes"])
     exp_b = orc.bias_update(biases0, sizes, B * S, K, Ks, 1e-3)
     assert torch.equal(moe.biases_N.detach().cpu(), exp_b)
@@ -159,6 +155,48 @@ def test_fused_wrapper_equals_router_then_experts(momoe, B, S, D, H, N, K, Ks, s
     assert torch.equal(a[5], b[5])
     assert cos(a[4].cpu(), b[4].cpu()) >= 0.99999 and max_rel(a[4].cpu(), b[4].cpu()) <= 1e-2
     assert cos(a[3].cpu(), b[3].cpu()) >= 0.99999
+
+
+def test_experts_honour_the_routing_tensors_they_are_given(momoe):
+    """`MoMoE` must read the `mask_NM` / `s_NM` it is called with (the reference reads s_NM in its down projection,
+    momoe/momoe.py:235-237, and the mask in find_used_experts, :821-842), not what the router attached to them:
+    doubled weights double the output exactly, a mask edited in place after routing is honoured, and the compact
+    short-cut is only taken for the router's own, unmodified tensors."""
+    from momoe.momoe import compact_routing_of
+    B, S, D, H, N, K, Ks = 1, 300, 256, 128, 8, 2, 0
+    dev = "cuda"
+    gen = torch.Generator().manual_seed(11)
+    W1 = (torch.randn(N, D, 2 * H, generator=gen) * 0.05).bfloat16().to(dev)
+    W2 = (torch.randn(N, H, D, generator=gen) * 0.05).bfloat16().to(dev)
+    Wg = (torch.randn(D, N, generator=gen) * 0.05).bfloat16().to(dev)
+    x = torch.randn(B, S, D, generator=gen).bfloat16().to(dev)
+    router = momoe.TopKRouter(D, N, K, Ks, Wg_DN=Wg)
+    layer = momoe.MoMoE(D, H, N, K, save_percent=0, Wl1_ND2H=W1, Wl2_NHD=W2)
+    biases = torch.zeros(N, device=dev)
+    with torch.no_grad():
+        _, mask_NM, s_NM = router(x, biases)
+        assert compact_routing_of(mask_NM, s_NM) is not None
+        y1, sizes1 = layer(x, mask_NM, s_NM)
+        s2 = 2.0 * s_NM
+        assert compact_routing_of(mask_NM, s2) is None
+        y2, _ = layer(x, mask_NM, s2)
+        assert torch.equal(y2.float(), 2.0 * y1.float())      # a power of two commutes with every rounding
+        # move token 0 from its first expert to an expert it did not select, as a capacity-dropping caller might
+        sel = torch.nonzero(mask_NM[:, 0]).flatten()
+        free = [e for e in range(N) if e not in sel.tolist()][0]
+        mask3 = mask_NM.clone()
+        s3 = s_NM.clone()
+        mask3[sel[0], 0], mask3[free, 0] = 0, 1
+        s3[free, 0], s3[sel[0], 0] = s3[sel[0], 0].item(), 0.0
+        y3, sizes3 = layer(x, mask3, s3)
+        assert int(sizes3[free]) == int(sizes1[free]) + 1 and int(sizes3[sel[0]]) == int(sizes1[sel[0]]) - 1
+        assert torch.equal(y3[0, 1:], y1[0, 1:]) and not torch.equal(y3[0, 0], y1[0, 0])
+        # the same edit done IN PLACE on the router's own tensors must be seen as well
+        mask_NM[sel[0], 0], mask_NM[free, 0] = 0, 1
+        assert compact_routing_of(mask_NM, s_NM) is None
+        y4, _ = layer(x, mask_NM, s3)
+        assert torch.equal(y4, y3)
+    _check_status()
 
 
 def test_forward_replays_as_a_cuda_graph(momoe):
@@ -237,3 +275,67 @@ def test_memory_held_for_backward_follows_save_percent(momoe):
     assert held[0] < 0.35 * ab_all                      # tables + weights cast + router state only
     assert 0.4 * ab_all < held[50] - held[0] < 0.75 * ab_all
     assert 0.9 * ab_all < held[100] - held[0] < 1.35 * ab_all
+
+
+def test_peer_handshake_gives_up_with_a_status_code(momoe):
+    """A wait on a peer that never arrives must run out, record status 301 and return, leaving the context usable
+    (failure detection without faulting a GPU: the flag simply is never set).  One GPU plays rank 0 of a 2-rank group
+    whose "peer" flag array is a second local buffer that nothing signals; the wait limit is shortened to ~20 ms."""
+    import ctypes as C
+    from momoe import _lib, ops
+    L = _lib.lib
+    dev = torch.device("cuda")
+    mine = torch.zeros(8, dtype=torch.int32, device=dev)
+    peer = torch.zeros(8, dtype=torch.int32, device=dev)
+    flags = (C.c_void_p * 2)(C.c_void_p(mine.data_ptr()), C.c_void_p(peer.data_ptr()))
+    status = ops.status_word(dev)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    before = L.momoe_ep_set_wait_limit(30_000_000)          # cycles: 15-25 ms at the SM clocks seen here
+    try:
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        _lib.check(L.momoe_ep_barrier(flags, 2, 0, 1, _lib.ptr(status), _lib.stream_ptr()), "barrier")
+        t1.record()
+        torch.cuda.synchronize()
+        assert 1.0 < t0.elapsed_time(t1) < 500.0             # it waited, and it gave up
+        assert peer.tolist()[0] == 1 and mine.tolist()[1] == 0      # our epoch reached the "peer"; nothing came back
+        with pytest.raises(RuntimeError, match="301"):
+            ops.check_status(dev)
+        ops.check_status(dev)                                 # cleared
+        # the same hand-shake completes at once when the peer's flag is there
+        mine[1] = 2
+        _lib.check(L.momoe_ep_barrier(flags, 2, 0, 2, _lib.ptr(status), _lib.stream_ptr()), "barrier")
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        # and the device still computes
+        assert float((torch.ones(1024, device=dev) * 2).sum()) == 2048.0
+    finally:
+        assert L.momoe_ep_set_wait_limit(before) == 30_000_000
+
+
+def test_device_error_is_reported_by_the_next_forward_without_a_sync(momoe):
+    """The asynchronous status report: a device-side error code left by one pass (here: a mask with a token that lacks
+    an expert) raises at a later forward call of the layer, with no `check_status` call by the user."""
+    from momoe import ops
+    from helpers import dense_from_topk, make_routing
+    M, N, K, D, H = 64, 8, 2, 64, 32
+    dev = "cuda"
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    topk_idx, topk_w = make_routing(M, N, K, seed=1)
+    mask_NM, s_NM = dense_from_topk(topk_idx, topk_w, N)
+    good_mask = mask_NM.clone()
+    mask_NM[:, 5] = 0                                         # token 5 has no expert
+    layer = momoe.MoMoE(D, H, N, K)
+    x = torch.randn(1, M, D, device=dev).bfloat16()
+    with torch.no_grad():
+        layer(x, mask_NM, s_NM)                               # records 201 on the device; nothing raises here
+        torch.cuda.synchronize()                              # (only so that the test is deterministic)
+        with pytest.raises(RuntimeError, match="201"):
+            for _ in range(3):                                # the report is picked up by one of the next calls
+                layer(x, good_mask, s_NM)
+                torch.cuda.synchronize()
+        layer(x, good_mask, s_NM)                             # and the layer is usable again
+    _check_status()

@@ -163,3 +163,31 @@ def test_gather_and_combine_rows(ops, M, N, K, D):
     # round trip: gathering then combining with K copies gives K*x up to one bf16 rounding
     back = ops.combine_rows(plan, xs, D)
     assert torch.equal(back, (x.float() * K).bfloat16())
+
+
+@pytest.mark.parametrize("M,n_rows,D", [(64, 200, 256), (4096, 10000, 2048), (7, 3, 72), (1000, 12345, 2176)])
+def test_gather_rows_from_a_row_table_only(ops, M, n_rows, D):
+    """`momoe_gather_rows` with `plan->pos_MK == NULL`: rows are fetched one by one from `plan->row_token` (the form
+    the expert-parallel NCCL transport uses with ad-hoc row tables, including rows marked -1).  Byte-exact against
+    `x[row_index]`, through the same helper that transport calls."""
+    from momoe import ep
+    g = torch.Generator().manual_seed(M + n_rows)
+    x = torch.randn(M, D, generator=g).bfloat16().cuda()
+    row_index = torch.randint(0, M, (n_rows,), generator=g).to(torch.int32)
+    row_index[::7] = -1                                          # padding rows: zeros
+    row_index = row_index.cuda()
+    got = ep._Rows.gather(x, row_index, n_rows)
+    torch.cuda.synchronize()
+    ri = row_index.long()
+    expect = torch.where((ri >= 0)[:, None], x[ri.clamp_min(0)], torch.zeros((), dtype=x.dtype, device="cuda"))
+    assert got.shape == (n_rows, D) and torch.equal(got, expect)
+    # and the matching combine with an ad-hoc position table
+    K = 3
+    Mc = n_rows // K
+    pos = torch.randperm(n_rows, generator=g)[:Mc * K].to(torch.int32).cuda()
+    y = ep._Rows.combine(got, pos, Mc, K)
+    ref = got[pos.long()].float().view(Mc, K, D)
+    acc = torch.zeros(Mc, D, device="cuda")
+    for k in range(K):
+        acc += ref[:, k]
+    assert torch.equal(y, acc.bfloat16())
