@@ -122,6 +122,15 @@ int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, v
 int momoe_combine_rows(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
                        momoe_stream_t stream);
 
+/* momoe_gather_rows / momoe_combine_rows with the grid held to max_blocks thread blocks of 256 threads (> 0), for
+ * callers that queue the row mover on a second stream BESIDE a grouped GEMM: one or two blocks per SM leave the GEMM's
+ * persistent thread blocks their registers and shared memory, and the mover's HBM traffic then hides behind the
+ * tensor-core work.  Same arithmetic and results as the plain entry points. */
+int momoe_gather_rows_beside(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
+                             int32_t max_blocks, momoe_stream_t stream);
+int momoe_combine_rows_beside(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
+                              int32_t max_blocks, momoe_stream_t stream);
+
 /* Up/gate grouped GEMM + SwiGLU: a = x W1[e][:, :H], b = x W1[e][:, H:], h = bf16(a * b * sigmoid(b)).
  * Replaces momoe/momoe.py:69-152.
  *   ab_mode 0: only h is written.

@@ -102,13 +102,47 @@ __device__ __forceinline__ void unpack_bf16(uint32_t v, float& lo, float& hi) {
 }
 __device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
-// 256-bit global loads (one full 32-byte sector per thread) for the a,b rows the dgrad-2 epilogue reads.
+// Store 32 consecutive fp32 values as bf16 to dst (16-byte aligned), keeping only columns < ncols_left.
+// ncols_left is a multiple of 8 by contract (all matrix widths are).
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float (&v)[32], int ncols_left) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        if (g * 8 < ncols_left) {
+            uint4 q;
+            q.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
+            q.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
+            q.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
+            q.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(dst + g * 8) = q;
+        }
+    }
+}
+// 256-bit global accesses (one full 32-byte sector per thread): half as many load/store instructions, which
+// matters because the row-per-thread pattern of the epilogues costs one tag look-up per thread and instruction.
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+                 "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
 __device__ __forceinline__ void ld_global_nc_256(const void* p, uint32_t (&v)[8]) {
     asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                  : "l"(p));
 }
-
+// Same as store_row32 for rows whose pitch is a multiple of 32 bytes and a fully valid 32-column chunk.
+__device__ __forceinline__ void store_row32_wide(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        uint32_t q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = pack_bf16(v[g * 16 + 2 * j], v[g * 16 + 2 * j + 1]);
+        st_global_256(dst + g * 16, q);
+    }
+}
+__device__ __forceinline__ void store_row32_auto(__nv_bfloat16* dst, const float (&v)[32], int ncols_left, bool wide) {
+    if (wide && ncols_left >= 32) store_row32_wide(dst, v);
+    else store_row32(dst, v, ncols_left);
+}
 // Work item -> coordinates of THIS CTA.
 // Row-tile modes: item = pair * n_nblk + nb; a pair is two consecutive 128-row tiles of one expert (the second may be
 // missing when the expert has an odd number of tiles).  Wgrad: item = (e * n_mblk + mb) * n_nblk + nb.
@@ -415,12 +449,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     } else {
         // ================================================================ epilogue (warps 2..9, both CTAs)
-        // Results leave through shared memory: a warp converts its 32 rows x 32 (dgrad-2: 16) columns to bf16, writes
-        // them into a slot of its 4 KiB staging area in the swizzled layout of the output's tensor map, and one lane
-        // hands the slot to a TMA store.  Global memory then sees full 64-byte (32-byte) row pieces written by the copy
-        // engine instead of one 32-byte access per thread and row, and tails (columns past the matrix width, rows past
-        // an expert's weight matrix) are clipped by the tensor map.  Slots rotate; a slot is rewritten once the store
-        // issued from it has finished READING it.
+        // Two ways out, chosen per mode by measurement on the headline layer.  Up/gate and dgrad-2 (one accumulator
+        // tile per 16 k-blocks, up to three outputs per element) leave through shared memory: a warp converts its
+        // 32 rows x 32 (dgrad-2: 16) columns to bf16, writes them into a slot of its 4 KiB staging area in the swizzled
+        // layout of the output's tensor map, and one lane hands the slot to a TMA store; tails are clipped by the
+        // tensor map; slots rotate, and a slot is rewritten once the store issued from it has finished READING it
+        // (dgrad-2: 0.78-0.81 ms with per-thread stores, 0.69-0.71 ms this way).  Down, dgrad-1 and the weight
+        // gradients (an accumulator tile every 8 k-blocks) store straight to global memory, one 32-byte piece per
+        // thread and row: the staging hop cost them 5-10 %.
         const int q = warp & 3;            // TMEM lane quarter this warp may read
         const int row = q * 32 + lane;     // accumulator row == TMEM lane
         const int half = (warp - 2) >> 2;  // which half of the tile's 32-column chunks this warp handles
@@ -482,8 +518,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int row0 = w.tile * TILE_M + q * 32;   // first of this warp's 32 output rows (row-tile modes)
             uint32_t r[32];
             if constexpr (MODE == MODE_DGRAD2) {
-                // The saved / recomputed a,b rows do not depend on the accumulator: the first 32-column chunk is
-                // fetched while the main loop is still running, each later chunk while the previous one is computed.
+                // 16 columns at a time.  The saved / recomputed a,b values do not depend on the accumulator: the first
+                // piece is fetched while the main loop is still running, each later one while its predecessor is
+                // computed.
+                constexpr int PIECES = PAIR_N / 16 / (EPI_WARPS / 4);   // 16-column pieces per warp
+                const int part = (warp - 2) >> 2;
                 const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
                 const int H = g.out_cols;
                 const bool wide = (H % 16) == 0;   // every a,b row starts on a 32-byte boundary
@@ -493,31 +532,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     (saved ? static_cast<size_t>(w.tile) : static_cast<size_t>(w.tile - n_saved)) * TILE_M + row;
                 const __nv_bfloat16* ap = (saved ? g.a_saved : g.a_recomp) + abrow * H;
                 const __nv_bfloat16* bp = (saved ? g.b_saved : g.b_recomp) + abrow * H;
-                const int c_begin = half * 4, c_end = half * 4 + 4;
-                uint4 na[4], nb4[4];
-                auto fetch = [&](int c) {
-                    const int col0 = w.nb * PAIR_N + c * 32;
-                    if (wide && w.valid && col0 + 32 <= H) {
-                        uint32_t t[8];
-#pragma unroll
-                        for (int i = 0; i < 2; ++i) {
-                            ld_global_nc_256(ap + col0 + i * 16, t);
-                            na[2 * i] = make_uint4(t[0], t[1], t[2], t[3]);
-                            na[2 * i + 1] = make_uint4(t[4], t[5], t[6], t[7]);
-                            ld_global_nc_256(bp + col0 + i * 16, t);
-                            nb4[2 * i] = make_uint4(t[0], t[1], t[2], t[3]);
-                            nb4[2 * i + 1] = make_uint4(t[4], t[5], t[6], t[7]);
-                        }
+                const int p_begin = part * PIECES, p_end = p_begin + PIECES;
+                uint32_t na[8], nb[8];
+                auto fetch = [&](int pc) {
+                    const int col = w.nb * PAIR_N + pc * 16;
+                    if (wide && w.valid && col + 16 <= H) {
+                        ld_global_nc_256(ap + col, na);
+                        ld_global_nc_256(bp + col, nb);
                         return;
                     }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const bool in = w.valid && col0 + i * 8 < H;
-                        na[i] = in ? __ldg(reinterpret_cast<const uint4*>(ap + col0 + i * 8)) : make_uint4(0, 0, 0, 0);
-                        nb4[i] = in ? __ldg(reinterpret_cast<const uint4*>(bp + col0 + i * 8)) : make_uint4(0, 0, 0, 0);
+                    for (int i = 0; i < 2; ++i) {
+                        const bool in = w.valid && col + i * 8 < H;
+                        const uint4 qa = in ? __ldg(reinterpret_cast<const uint4*>(ap + col + i * 8)) : make_uint4(0, 0, 0, 0);
+                        const uint4 qb = in ? __ldg(reinterpret_cast<const uint4*>(bp + col + i * 8)) : make_uint4(0, 0, 0, 0);
+                        na[4 * i] = qa.x; na[4 * i + 1] = qa.y; na[4 * i + 2] = qa.z; na[4 * i + 3] = qa.w;
+                        nb[4 * i] = qb.x; nb[4 * i + 1] = qb.y; nb[4 * i + 2] = qb.z; nb[4 * i + 3] = qb.w;
                     }
                 };
-                fetch(c_begin);
+                fetch(p_begin);
                 const float wgt = w.valid ? __ldg(g.row_weight + grow) : 0.0f;
                 ok = mbar_wait(smem_u32(&bar_acc_full[ab]), aphase, abortp, g.status, DEV_TIMEOUT_EPILOGUE);
                 if (!ok) break;
@@ -525,56 +558,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (w.valid) {
                     float gs = 0.0f;
 #pragma unroll 1
-                    for (int c = c_begin; c < c_end; ++c) {
-                        const int col0 = w.nb * PAIR_N + c * 32;
-                        if (col0 >= H) break;
-                        uint4 ca[4], cb[4];
+                    for (int pc = p_begin; pc < p_end; ++pc) {
+                        const int col = w.nb * PAIR_N + pc * 16;
+                        if (col >= H) break;
+                        uint32_t ca[8], cb[8], r16[16];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) { ca[i] = na[i]; cb[i] = nb4[i]; }
-                        if (c + 1 < c_end) fetch(c + 1);
-                        tmem_ld32(taddr + c * 32, r);
+                        for (int i = 0; i < 8; ++i) { ca[i] = na[i]; cb[i] = nb[i]; }
+                        if (pc + 1 < p_end) fetch(pc + 1);
+                        tmem_ld16(taddr + pc * 16, r16);
                         tmem_ld_wait();
+                        uint32_t o1[8], o2[8], o3[8];
 #pragma unroll
-                        for (int i2 = 0; i2 < 2; ++i2) {   // 16 columns at a time: compute, pack, stage, store
-                            uint32_t o1[8], o2[8], o3[8];
-#pragma unroll
-                            for (int ii = 0; ii < 2; ++ii) {
-                                const int i = i2 * 2 + ii;
-                                const uint32_t pa[4] = {ca[i].x, ca[i].y, ca[i].z, ca[i].w};
-                                const uint32_t pb[4] = {cb[i].x, cb[i].y, cb[i].z, cb[i].w};
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    float a0, a1, b0, b1;
-                                    unpack_bf16(pa[j], a0, a1);
-                                    unpack_bf16(pb[j], b0, b1);
-                                    const float g0 = __uint_as_float(r[i * 8 + 2 * j]);
-                                    const float g1 = __uint_as_float(r[i * 8 + 2 * j + 1]);
-                                    const float s0 = sigmoidf_fast(b0), s1 = sigmoidf_fast(b1);
-                                    const float h0 = bf16_round(a0 * b0 * s0), h1 = bf16_round(a1 * b1 * s1);
-                                    gs = fmaf(g0, h0, gs);
-                                    gs = fmaf(g1, h1, gs);
-                                    const float gh0 = wgt * g0, gh1 = wgt * g1;
-                                    o1[ii * 4 + j] = pack_bf16(gh0 * b0 * s0, gh1 * b1 * s1);
-                                    o2[ii * 4 + j] = pack_bf16(gh0 * a0 * s0 * fmaf(b0, 1.0f - s0, 1.0f),
-                                                               gh1 * a1 * s1 * fmaf(b1, 1.0f - s1, 1.0f));   // gate half
-                                    o3[ii * 4 + j] = pack_bf16(wgt * h0, wgt * h1);
-                                }
-                            }
-                            const int col = col0 + i2 * 16;
-                            if (col >= H) continue;   // uniform across the warp
-                            // gz is addressed as [rows, 2, H] so that the linear half is clipped at H
-                            uint32_t slot = slot_acquire();
-                            slot_write32(slot, o1);
-                            slot_store3d(&tmO0, slot, col, 0, row0);
-                            slot = slot_acquire();
-                            slot_write32(slot, o2);
-                            slot_store3d(&tmO0, slot, col, 1, row0);
-                            slot = slot_acquire();
-                            slot_write32(slot, o3);
-                            slot_store2d(&tmO1, slot, col, row0);
+                        for (int j = 0; j < 8; ++j) {
+                            float a0, a1, b0, b1;
+                            unpack_bf16(ca[j], a0, a1);
+                            unpack_bf16(cb[j], b0, b1);
+                            const float g0 = __uint_as_float(r16[2 * j]);
+                            const float g1 = __uint_as_float(r16[2 * j + 1]);
+                            const float s0 = sigmoidf_fast(b0), s1 = sigmoidf_fast(b1);
+                            const float h0 = bf16_round(a0 * b0 * s0), h1 = bf16_round(a1 * b1 * s1);
+                            gs = fmaf(g0, h0, gs);
+                            gs = fmaf(g1, h1, gs);
+                            const float gh0 = wgt * g0, gh1 = wgt * g1;
+                            o1[j] = pack_bf16(gh0 * b0 * s0, gh1 * b1 * s1);
+                            o2[j] = pack_bf16(gh0 * a0 * s0 * fmaf(b0, 1.0f - s0, 1.0f),
+                                              gh1 * a1 * s1 * fmaf(b1, 1.0f - s1, 1.0f));   // gate half
+                            o3[j] = pack_bf16(wgt * h0, wgt * h1);
                         }
+                        // gz is addressed as [rows, 2, H] so that the linear half is clipped at H
+                        uint32_t slot = slot_acquire();
+                        slot_write32(slot, o1);
+                        slot_store3d(&tmO0, slot, col, 0, row0);
+                        slot = slot_acquire();
+                        slot_write32(slot, o2);
+                        slot_store3d(&tmO0, slot, col, 1, row0);
+                        slot = slot_acquire();
+                        slot_write32(slot, o3);
+                        slot_store2d(&tmO1, slot, col, row0);
                     }
-                    g.gs_part[(grow * g.n_nblk + w.nb) * 2 + half] = gs;   // two partial sums per 256-column block
+                    g.gs_part[(grow * g.n_nblk + w.nb) * 2 + part] = gs;   // two partial sums per 256-column block
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -588,6 +610,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (!ok) break;
             tc_fence_after();
             uint32_t p[16];
+            float v[32];
+            const bool wide = (g.out_cols % 16) == 0;   // every output row starts on a 32-byte boundary
 
             if constexpr (MODE == MODE_UP) {
                 const int n_saved = __ldg(g.sched + SCHED_N_SAVED_TILES);
@@ -631,46 +655,42 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                 }
             } else if constexpr (MODE == MODE_DOWN || MODE == MODE_DGRAD1) {
+                const size_t grow = static_cast<size_t>(w.tile) * TILE_M + row;
                 if (w.valid) {
                     float wgt = 1.0f;
-                    if constexpr (MODE == MODE_DOWN) wgt = __ldg(g.row_weight + static_cast<size_t>(w.tile) * TILE_M + row);
+                    if constexpr (MODE == MODE_DOWN) wgt = __ldg(g.row_weight + grow);
 #pragma unroll 1
                     for (int c = half * 4; c < half * 4 + 4; ++c) {
                         const int col0 = w.nb * PAIR_N + c * 32;
-                        if (col0 >= g.out_cols) break;
+                        const int left = g.out_cols - col0;
+                        if (left <= 0) break;
                         tmem_ld32(taddr + c * 32, r);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            p[i] = pack_bf16(__uint_as_float(r[2 * i]) * wgt, __uint_as_float(r[2 * i + 1]) * wgt);
-                        const uint32_t slot = slot_acquire();
-                        slot_write64(slot, p);
-                        slot_store2d(&tmO0, slot, col0, row0);
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * wgt;
+                        store_row32_auto(g.out0 + grow * g.out_cols + col0, v, left, wide);
                     }
                 }
             } else if constexpr (MODE == MODE_DGRAD2) {
-                // handled above: its operand prefetch starts before the accumulator wait
+                // handled below: its operand prefetch starts before the accumulator wait
             } else {  // MODE_WGRAD
-                const int orow0 = w.mb * 256 + static_cast<int>(cta_rank) * TILE_M + q * 32;
-                if (orow0 < g.out_rows) {   // rows past the matrix inside the box are clipped by the tensor map
+                const int orow = w.mb * 256 + static_cast<int>(cta_rank) * TILE_M + row;
+                __nv_bfloat16* dst = g.out0 + (static_cast<size_t>(w.e) * g.out_rows + orow) * g.out_cols;
 #pragma unroll 1
-                    for (int c = half * 4; c < half * 4 + 4; ++c) {
-                        const int col0 = w.nb * PAIR_N + c * 32;
-                        if (col0 >= g.out_cols) break;
-                        if (w.nkb > 0) {
-                            tmem_ld32(taddr + c * 32, r);
-                            tmem_ld_wait();
+                for (int c = half * 4; c < half * 4 + 4; ++c) {
+                    const int col0 = w.nb * PAIR_N + c * 32;
+                    const int left = g.out_cols - col0;
+                    if (left <= 0) break;
+                    if (w.nkb > 0) {
+                        tmem_ld32(taddr + c * 32, r);
+                        tmem_ld_wait();
 #pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                p[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                        } else {
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                    } else {
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) p[i] = 0u;
-                        }
-                        const uint32_t slot = slot_acquire();
-                        slot_write64(slot, p);
-                        slot_store3d(&tmO0, slot, col0, orow0, w.e);
+                        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                     }
+                    if (orow < g.out_rows) store_row32_auto(dst + col0, v, left, wide);
                 }
             }
             // hand the accumulator buffer back to the MMA thread of the leader CTA
@@ -862,8 +882,7 @@ extern "C" __attribute__((visibility("default"))) int momoe_down_scale(const mom
     g.out_cols = D;
     g.out0 = static_cast<__nv_bfloat16*>(y_sorted);
     OutMaps o;
-    if ((rc = out_map_2d(o, 0, y_sorted, plan->rows_capacity, D)) != MOMOE_OK) return rc;
-    o.m[1] = o.m[2] = o.m[0];
+    o.m[0] = o.m[1] = o.m[2] = tmA;   // this mode stores its results directly
     return launch<MODE_DOWN>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
 }
 
@@ -943,8 +962,7 @@ extern "C" __attribute__((visibility("default"))) int momoe_dgrad1(const momoe_p
     g.out_cols = D;
     g.out0 = static_cast<__nv_bfloat16*>(gx_sorted);
     OutMaps o;
-    if ((rc = out_map_2d(o, 0, gx_sorted, plan->rows_capacity, D)) != MOMOE_OK) return rc;
-    o.m[1] = o.m[2] = o.m[0];
+    o.m[0] = o.m[1] = o.m[2] = tmA;   // this mode stores its results directly
     return launch<MODE_DGRAD1>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
 }
 
@@ -979,9 +997,7 @@ static int wgrad_impl(const momoe_plan_t* plan, const void* a, int32_t X, bool a
     g.out_cols = Y;
     g.out0 = static_cast<__nv_bfloat16*>(dW_NXY);
     OutMaps o;
-    // [N, X, Y] in pieces of 32 rows x 32 columns of one expert: rows past X are clipped, not written into expert e+1
-    if ((rc = encode_tmap_3d(&o.m[0], dW_NXY, plan->N, X, Y, 32, 32, TMAP_SWIZZLE_64B)) != MOMOE_OK) return rc;
-    o.m[1] = o.m[2] = o.m[0];
+    o.m[0] = o.m[1] = o.m[2] = tmA;   // this mode stores its results directly
     return launch<MODE_WGRAD>(tmA, tmB, o, g, static_cast<cudaStream_t>(stream));
 }
 

@@ -30,16 +30,21 @@ def run_case(transport, case, rank, world, dev, momoe, ep, ops, cos, max_rel):
                     Wl1_ND2H=W1.to(dev), Wl2_NHD=W2.to(dev))
     with torch.no_grad():
         ref.biases_N.copy_(biases.to(dev))
+    # (b) expert parallel, own shard
+    # the sharded layer starts from other weights and takes the single-GPU layer's checkpoint with a plain
+    # load_state_dict: keys as in the reference, every rank keeps its own block of the [N, ...] expert tensors
+    moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3,
+                               Wg_DN=torch.zeros(D, N, device=dev), Wl1_ND2H=torch.zeros(Nl, D, 2 * H, device=dev),
+                               Wl2_NHD=torch.zeros(Nl, H, D, device=dev), transport=transport,
+                               capacity_factor=float(world))   # room for any routing, however skewed
+    ckpt = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    res = moe.load_state_dict(ckpt)
+    assert not res.missing_keys and not res.unexpected_keys
+    assert torch.equal(moe.Wl1_ND2H, W1[rank * Nl:(rank + 1) * Nl].to(dev))
+    assert torch.equal(moe.biases_N, biases.to(dev))
     xa = x_all.reshape(1, world * Mr, D).to(dev).requires_grad_(True)
     ya = ref(xa)
     ya.backward(gy_all.reshape(1, world * Mr, D).to(dev))
-    # (b) expert parallel, own shard
-    moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3, Wg_DN=Wg.to(dev),
-                               Wl1_ND2H=W1[rank * Nl:(rank + 1) * Nl].to(dev),
-                               Wl2_NHD=W2[rank * Nl:(rank + 1) * Nl].to(dev), transport=transport,
-                               capacity_factor=float(world))   # room for any routing, however skewed
-    with torch.no_grad():
-        moe.biases_N.copy_(biases.to(dev))
     xr = x_all[rank].to(dev).requires_grad_(True)
     yr = moe(xr)
     yr.backward(gy_all[rank].to(dev))
@@ -91,11 +96,14 @@ def main():
     x = torch.randn(1, 4096, D, generator=g).bfloat16().to(dev).requires_grad_(True)
     moe(x).sum().backward()
     torch.cuda.synchronize()
+    # nobody calls check_status: the next forward pass of the layer must raise by itself
     try:
-        ops.check_status(dev)
+        moe(x)
         raise AssertionError("overflow of the expert-parallel buffers was not reported")
     except RuntimeError as err:
         assert "302" in str(err), err
+    torch.cuda.synchronize()
+    ops.check_status(dev)          # reported once, then cleared
     if rank == 0:
         print("ep overflow reported ok", flush=True)
     dist.barrier()

@@ -207,3 +207,35 @@ def test_dispatch_schedule_visits_every_row_once_and_spreads_destinations(world,
             w0 = [d for wid, it, d, off in visits if wid == 0][:world]
             if min(seg_len) > (world * warps_total) // world:
                 assert len(set(w0)) == world
+
+
+def test_peer_buffers_refuse_a_second_forward_before_the_backward():
+    """The peer transport's buffers hold one step at a time (host logic only; no device memory is touched here): a
+    forward pass that needs a backward pass blocks the next forward until that backward pass has run or its autograd
+    graph has been dropped; passes under no_grad never block."""
+    import gc
+    import sys
+    import weakref
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(os.path.dirname(here), "momoe-impl_b200"))
+    from momoe import ep
+    bufs = ep.PeerBuffers.__new__(ep.PeerBuffers)      # the bookkeeping without the symmetric allocations
+    bufs._step, bufs._pending = 0, 0
+    s1 = bufs.begin_step(needs_backward=False)         # inference passes do not hold the buffers
+    s2 = bufs.begin_step(needs_backward=True)
+    assert (s1, s2) == (1, 2)
+    with pytest.raises(RuntimeError, match="backward pass of the previous forward"):
+        bufs.begin_step(needs_backward=True)
+    with pytest.raises(RuntimeError, match="backward pass of the previous forward"):
+        bufs.begin_step(needs_backward=False)          # an evaluation pass in between would overwrite them as well
+    bufs.end_step(s1)                                  # a stale step id releases nothing
+    with pytest.raises(RuntimeError):
+        bufs.begin_step(needs_backward=True)
+    bufs.end_step(s2)                                  # the backward pass ran
+    s3 = bufs.begin_step(needs_backward=True)
+    # an output dropped without a backward pass: the token dies with the graph and releases the buffers
+    tok = ep._StepToken()
+    weakref.finalize(tok, bufs.end_step, s3)
+    del tok
+    gc.collect()
+    assert bufs.begin_step(needs_backward=True) == s3 + 1

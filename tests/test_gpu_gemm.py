@@ -290,15 +290,19 @@ def test_token_major_entry_points_match_expert_major(ops, M, N, K, D, H, skew, s
     assert float(out[True]["gz"][~real].float().abs().sum()) == 0.0
     assert float(out[True]["hs"][~real].float().abs().sum()) == 0.0
     # and the layer through the public sequences, both settings of the switch
-    res = {}
-    for fused in (True, False):
-        ops.FUSED_GATHER = fused
+    # (fused gathers; separate gathers on one stream; separate gathers with the movers beside the GEMMs on a second
+    # stream): identical bits
+    res = []
+    keep = (ops.FUSED_GATHER, ops.OVERLAP)
+    for fused, overlap in ((True, False), (False, False), (False, True)):
+        ops.FUSED_GATHER, ops.OVERLAP = fused, overlap
         try:
             y, a_save, b_save = ops.experts_forward(plan, x, W1, W2)
-            res[fused] = (y,) + tuple(ops.experts_backward(plan, gy, x, W1, W2, a_save, b_save, need_gs_dense=True))
+            res.append((y,) + tuple(ops.experts_backward(plan, gy, x, W1, W2, a_save, b_save, need_gs_dense=True)))
         finally:
-            ops.FUSED_GATHER = True
+            ops.FUSED_GATHER, ops.OVERLAP = keep
     torch.cuda.synchronize()
     ops.check_status()
-    for a, b in zip(res[True], res[False]):
-        assert torch.equal(a, b)
+    for other in res[1:]:
+        for a, b in zip(res[0], other):
+            assert torch.equal(a, b)
