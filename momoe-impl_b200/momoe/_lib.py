@@ -48,6 +48,7 @@ _PROTOS = {
     "momoe_gather_rows_beside": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp]),
     "momoe_combine_rows_beside": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp]),
     "momoe_up_swiglu": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
+    "momoe_up_swiglu_gather": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "momoe_up_swiglu_tokens": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "momoe_down_scale": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_up_swiglu_decode": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),

@@ -231,6 +231,12 @@ def combine_rows(plan, src_sorted, cols):
 # separate `momoe_gather_rows` launches in front of the GEMMs.
 FUSED_GATHER = os.environ.get("MOMOE_B200_FUSED_GATHER", "0") == "1"
 
+# The up/gate kernel gathers its own A operand: four extra warps per thread block copy the token rows into expert-major
+# order while the tensor cores work on tiles whose rows are already there (`momoe_up_swiglu_gather`), so the forward pass
+# and the recomputation in the backward pass have no separate `momoe_gather_rows` launch for x.  MOMOE_B200_MOVERS=0
+# restores the separate launch.
+MOVERS = os.environ.get("MOMOE_B200_MOVERS", "1") == "1"
+
 # Forward-only calls with at most this many rows per expert on average take the weight-streaming kernels
 # (momoe_up_swiglu_decode / momoe_down_scale_decode) instead of the 256-row tile kernels.
 DECODE_MAX_AVG_ROWS = int(os.environ.get("MOMOE_B200_DECODE_ROWS", "16"))
@@ -261,6 +267,12 @@ def experts_forward(plan, x_MD, W1, W2, inference=False):
     if FUSED_GATHER:
         _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu_tokens, plan.ref, ptr(x_MD), ptr(W1), ptr(h), ptr(a_save),
               ptr(b_save), mode, stream_ptr())
+    elif MOVERS:
+        x_sorted = torch.empty((plan.rows_capacity, D), **bf)
+        ready = torch.empty(plan.tile_capacity, dtype=torch.int32, device=dev)
+        _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu_gather, plan.ref, ptr(x_MD), ptr(x_sorted), ptr(ready), ptr(W1),
+              ptr(h), ptr(a_save), ptr(b_save), mode, stream_ptr())
+        del x_sorted, ready
     else:
         x_sorted = gather_rows(plan, x_MD, D)
         _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), ptr(h), ptr(a_save),
@@ -318,13 +330,21 @@ def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=Tru
                 ev[1].record(side)
         else:
             _call("momoe_gather_rows", 1, lib.momoe_gather_rows, plan.ref, ptr(g_MD), D, ptr(g_src), stream_ptr())
-        x_src = gather_rows(plan, x_MD, D)
+        movers = MOVERS and plan.recomp_tile_capacity > 0
+        x_src = torch.empty((plan.rows_capacity, D), **bf) if movers else gather_rows(plan, x_MD, D)
     a_rec = b_rec = None
     if plan.recomp_tile_capacity > 0:
         a_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
         b_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
-        _call("momoe_up_swiglu (recompute)", 1, up, plan.ref, ptr(x_src), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2,
-              stream_ptr())
+        if not fused and movers:
+            # the recomputation launch gathers x itself; x_src is complete when it has finished (the W1 gradient
+            # reads it)
+            ready = torch.empty(plan.tile_capacity, dtype=torch.int32, device=dev)
+            _call("momoe_up_swiglu (recompute)", 1, lib.momoe_up_swiglu_gather, plan.ref, ptr(x_MD), ptr(x_src),
+                  ptr(ready), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2, stream_ptr())
+        else:
+            _call("momoe_up_swiglu (recompute)", 1, up, plan.ref, ptr(x_src), ptr(W1), None, ptr(a_rec), ptr(b_rec),
+                  2, stream_ptr())
     if overlap:
         main.wait_event(ev[1])
     n_part = 2 * ((H + 255) // 256)   # two partial sums per 256-column block (momoe_dgrad2_swiglu_bwd)
