@@ -122,15 +122,6 @@ int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, v
 int momoe_combine_rows(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
                        momoe_stream_t stream);
 
-/* momoe_gather_rows / momoe_combine_rows with the grid held to max_blocks thread blocks of 256 threads (> 0), for
- * callers that queue the row mover on a second stream BESIDE a grouped GEMM: one or two blocks per SM leave the GEMM's
- * persistent thread blocks their registers and shared memory, and the mover's HBM traffic then hides behind the
- * tensor-core work.  Same arithmetic and results as the plain entry points. */
-int momoe_gather_rows_beside(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
-                             int32_t max_blocks, momoe_stream_t stream);
-int momoe_combine_rows_beside(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
-                              int32_t max_blocks, momoe_stream_t stream);
-
 /* Up/gate grouped GEMM + SwiGLU: a = x W1[e][:, :H], b = x W1[e][:, H:], h = bf16(a * b * sigmoid(b)).
  * Replaces momoe/momoe.py:69-152.
  *   ab_mode 0: only h is written.
@@ -139,21 +130,6 @@ int momoe_combine_rows_beside(const momoe_plan_t* plan, const void* src_sorted, 
  *              (tile - sched[1])*128 of a_out/b_out; h_sorted may be NULL. */
 int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted, const void* W1_ND2H, void* h_sorted,
                     void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream);
-
-/* momoe_gather_rows and momoe_up_swiglu in ONE launch, with the gather hidden behind the tensor-core work: four
- * extra warps per thread block copy x_MD[row_token[r], :] to x_sorted[r, :] (zeros on padding rows) for all padded
- * rows in ascending order and count finished rows per 128-row tile in tile_ready; the kernel's TMA producer loads a
- * tile of x_sorted once its 128 rows are there.  All thread blocks of the launch are resident and the copying warps
- * wait for nothing, so the counters always fill; the producer's wait is bounded all the same (status 101).
- *   x_MD        token-major input bf16 [plan->M, D]
- *   x_sorted    OUT: the expert-major copy [rows_capacity, D], complete when the launch has finished (the backward
- *               pass reuses it for the W1 gradient)
- *   tile_ready  scratch int32[momoe_tile_capacity(M, K, N)], zeroed by this call on `stream`
- * Other arguments and results exactly as momoe_up_swiglu on the finished x_sorted.  Replaces momoe/momoe.py:69-152
- * including the row fetch at :116-118, which the reference also performs inside its kernel. */
-int momoe_up_swiglu_gather(const momoe_plan_t* plan, const void* x_MD, void* x_sorted, int32_t* tile_ready,
-                           const void* W1_ND2H, void* h_sorted, void* a_out, void* b_out, int32_t ab_mode,
-                           momoe_stream_t stream);
 
 /* momoe_up_swiglu with the row gather folded into the GEMM's operand loads, as the reference's kernel does
  * (momoe/momoe.py:116-118: `x` rows are fetched through the expert-major index inside lin1_kernel).  x_MD is the

@@ -37,6 +37,7 @@
 namespace momoe {
 
 constexpr int EPI_WARPS = 8;
+constexpr int CTA_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int PAIR_N = 256;                          // tile width of a CTA pair
 constexpr int A_BYTES = TILE_M * TILE_K * 2;         // 16 KiB: this CTA's 128 rows x 64 k
 constexpr int B_BYTES = (PAIR_N / 2) * TILE_K * 2;   // 16 KiB: this CTA's half of B x 64 k
@@ -82,22 +83,10 @@ struct GemmArgs {
     const int* rows;
     int gather;
     int n_tokens;
-    // Mover warps (up/gate only, tile_ready != nullptr): copy mover_src[rows[r], :] to mover_dst[r, :] (16-byte units,
-    // mover_vec per row; zeros on padding rows) for every padded row r, and count finished rows per 128-row tile in
-    // tile_ready (zeroed by the host side before the launch).  The TMA producer reads a tile of mover_dst (= the A
-    // operand) once its count has reached 128.
-    const uint4* mover_src;
-    uint4* mover_dst;
-    int mover_vec;
-    int* tile_ready;
 };
 
 template <int MODE>
 struct Cfg {
-    // Up/gate can carry four more warps that gather the A operand's rows into expert-major order while the tiles run
-    // (see the mover role in the kernel); the other modes have none.
-    static constexpr int MOVER_WARPS = (MODE == MODE_UP) ? 4 : 0;
-    static constexpr int THREADS = 64 + 32 * EPI_WARPS + 32 * MOVER_WARPS;
     static constexpr bool A_MN = (MODE == MODE_WGRAD);
     static constexpr bool B_MN = (MODE == MODE_UP || MODE == MODE_DOWN || MODE == MODE_WGRAD);
 };
@@ -198,7 +187,7 @@ __device__ __forceinline__ Work decode_work(const GemmArgs& g, int item, uint32_
 }
 
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg<MODE>::THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmO0, const __grid_constant__ CUtensorMap tmO1,
                     const __grid_constant__ CUtensorMap tmO2, const GemmArgs g) {
@@ -224,8 +213,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int total_items;
     if constexpr (MODE == MODE_WGRAD) total_items = g.n_experts * g.n_mblk * g.n_nblk;
     else total_items = __ldg(g.sched + SCHED_N_PAIRS) * g.n_nblk;
-    if (g.tile_ready == nullptr && (total_items <= 0 || cluster_id >= total_items))
-        return;  // both CTAs of the cluster leave together; with movers every CTA stays: it has rows to move
+    if (total_items <= 0 || cluster_id >= total_items) return;  // both CTAs of the cluster leave together
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -359,20 +347,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            int ready_tile = -1;   // last tile whose rows are known to be in place (mover launches)
             for (int item = cluster_id; ok && item < total_items; item += n_clusters) {
                 const Work w = decode_work<MODE>(g, item, cta_rank);
                 if (w.skip) continue;
-                if constexpr (MODE == MODE_UP) {
-                    if (g.tile_ready != nullptr && w.valid && w.tile != ready_tile) {
-                        // rows of this tile are being written by mover warps of this same launch (all CTAs are
-                        // resident and movers never wait, so the count always gets there); bounded like every wait
-                        ok = flag_wait_ge(g.tile_ready + w.tile, TILE_M, abortp, g.status, DEV_TIMEOUT_PRODUCER);
-                        if (!ok) break;
-                        fence_proxy_async_all();   // rows written through the generic proxy, read by TMA
-                        ready_tile = w.tile;
-                    }
-                }
                 for (int kb = 0; kb < w.nkb; ++kb) {
                     ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, g.status, DEV_TIMEOUT_PRODUCER);
                     if (!ok) break;
@@ -470,7 +447,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
             }
         }
-    } else if (warp < 2 + EPI_WARPS) {
+    } else {
         // ================================================================ epilogue (warps 2..9, both CTAs)
         // Two ways out, chosen per mode by measurement on the headline layer.  Up/gate and dgrad-2 (one accumulator
         // tile per 16 k-blocks, up to three outputs per element) leave through shared memory: a warp converts its
@@ -727,48 +704,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // the staging area must outlive every store issued from it
         if (lane == 0) bulk_wait_all<0>();
         __syncwarp();
-    } else {
-        // ================================================================ movers (warps 10..13, up/gate only)
-        // Row r of the expert-major A operand is a copy of row rows[r] of the token-major input.  These warps make the
-        // copies while the tensor cores work on tiles whose rows are already in place: one warp per row, rows handed
-        // out round-robin over all mover warps of the grid so that tiles complete in ascending order, which is the
-        // order the work items consume them in.  After a row, one lane publishes it with a release increment of the
-        // tile's counter.  Movers wait for nothing, so every counter reaches 128.
-        if constexpr (C::MOVER_WARPS > 0) {
-            if (g.tile_ready != nullptr) {
-                const int n_movers = static_cast<int>(gridDim.x) * C::MOVER_WARPS;
-                const int mw = static_cast<int>(blockIdx.x) * C::MOVER_WARPS + (warp - 2 - EPI_WARPS);
-                const int n_rows = __ldg(g.sched + SCHED_PAD_ROWS);
-                const int vec = g.mover_vec;
-                const bool wide = (vec % 2) == 0 &&
-                                  ((reinterpret_cast<uintptr_t>(g.mover_src) | reinterpret_cast<uintptr_t>(g.mover_dst)) & 31) == 0;
-                for (int r = mw; r < n_rows; r += n_movers) {
-                    const int tok = __ldg(g.rows + r);
-                    uint4* d = g.mover_dst + static_cast<size_t>(r) * vec;
-                    if (tok >= 0 && tok < g.n_tokens) {
-                        const uint4* sp = g.mover_src + static_cast<size_t>(tok) * vec;
-                        if (wide) {
-                            const int n32 = vec >> 1;   // 32-byte pieces per row, four per lane in flight
-                            for (int c0 = lane; c0 < n32; c0 += 128) {
-                                uint32_t t[4][8];
-#pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    if (c0 + j * 32 < n32) ld_global_nc_256(sp + 2 * (c0 + j * 32), t[j]);
-#pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    if (c0 + j * 32 < n32) st_global_256(d + 2 * (c0 + j * 32), t[j]);
-                            }
-                        } else {
-                            for (int c = lane; c < vec; c += 32) d[c] = __ldg(sp + c);
-                        }
-                    } else {
-                        for (int c = lane; c < vec; c += 32) d[c] = make_uint4(0, 0, 0, 0);
-                    }
-                    __syncwarp();
-                    if (lane == 0) red_release_add(g.tile_ready + (r / TILE_M), 1);
-                }
-            }
-        }
     }
 
     // ---- teardown: both CTAs meet (the peer's shared memory and TMEM stay alive until the leader's last MMA has
@@ -819,7 +754,7 @@ static int resident_pairs() {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(static_cast<unsigned>(sm_count() / 2 * 2));
-        cfg.blockDim = dim3(Cfg<MODE>::THREADS);
+        cfg.blockDim = dim3(CTA_THREADS);
         cfg.dynamicSmemBytes = SMEM_BYTES;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -863,7 +798,7 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const OutMaps&
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const int grid = 2 * resident_pairs<MODE>();
-    grouped_gemm_kernel<MODE><<<grid, Cfg<MODE>::THREADS, SMEM_BYTES, stream>>>(tmA, tmB, o.m[0], o.m[1], o.m[2], g);
+    grouped_gemm_kernel<MODE><<<grid, CTA_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, o.m[0], o.m[1], o.m[2], g);
     return cudaGetLastError() == cudaSuccess ? MOMOE_OK : MOMOE_ERR_CUDA;
 }
 
@@ -886,15 +821,10 @@ static int a_operand(const momoe_plan_t* plan, const void* src, int cols, bool t
 }
 
 static int up_swiglu_impl(const momoe_plan_t* plan, const void* x, bool tokens, const void* W1_ND2H, void* h_sorted,
-                          void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream,
-                          const void* mover_src = nullptr, int32_t* tile_ready = nullptr) {
+                          void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream) {
     int rc = check_plan(plan);
     if (rc != MOMOE_OK) return rc;
     if (x == nullptr || W1_ND2H == nullptr) return MOMOE_ERR_ARG;
-    if ((mover_src == nullptr) != (tile_ready == nullptr)) return MOMOE_ERR_ARG;
-    if (mover_src != nullptr &&
-        (tokens || plan->row_token == nullptr || (reinterpret_cast<uintptr_t>(mover_src) & 15) != 0))
-        return MOMOE_ERR_ARG;
     if (ab_mode < 0 || ab_mode > 2) return MOMOE_ERR_ARG;
     if (ab_mode != 2 && h_sorted == nullptr) return MOMOE_ERR_ARG;
     if (ab_mode != 0 && (a_out == nullptr || b_out == nullptr)) return MOMOE_ERR_ARG;
@@ -912,18 +842,6 @@ static int up_swiglu_impl(const momoe_plan_t* plan, const void* x, bool tokens, 
     g.out0 = static_cast<__nv_bfloat16*>(h_sorted);
     g.out1 = static_cast<__nv_bfloat16*>(a_out);
     g.out2 = static_cast<__nv_bfloat16*>(b_out);
-    if (mover_src != nullptr) {
-        // x (= the A operand's buffer) is filled by this launch's mover warps from the token-major mover_src
-        g.rows = plan->row_token;
-        g.n_tokens = plan->M;
-        g.mover_src = static_cast<const uint4*>(mover_src);
-        g.mover_dst = static_cast<uint4*>(const_cast<void*>(x));
-        g.mover_vec = D / 8;
-        g.tile_ready = tile_ready;
-        if (cudaMemsetAsync(tile_ready, 0, sizeof(int32_t) * static_cast<size_t>(plan->rows_capacity / TILE_M),
-                            static_cast<cudaStream_t>(stream)) != cudaSuccess)
-            return MOMOE_ERR_CUDA;
-    }
     OutMaps o;
     o.m[0] = o.m[1] = o.m[2] = tmA;
     if (h_sorted != nullptr && (rc = out_map_2d(o, 0, h_sorted, plan->rows_capacity, H)) != MOMOE_OK) return rc;
@@ -940,13 +858,6 @@ static int up_swiglu_impl(const momoe_plan_t* plan, const void* x, bool tokens, 
 MOMOE_API int momoe_up_swiglu(const momoe_plan_t* plan, const void* x_sorted, const void* W1_ND2H, void* h_sorted,
                               void* a_out, void* b_out, int32_t ab_mode, momoe_stream_t stream) {
     return up_swiglu_impl(plan, x_sorted, false, W1_ND2H, h_sorted, a_out, b_out, ab_mode, stream);
-}
-
-MOMOE_API int momoe_up_swiglu_gather(const momoe_plan_t* plan, const void* x_MD, void* x_sorted, int32_t* tile_ready,
-                                     const void* W1_ND2H, void* h_sorted, void* a_out, void* b_out, int32_t ab_mode,
-                                     momoe_stream_t stream) {
-    if (x_sorted == nullptr) return MOMOE_ERR_ARG;
-    return up_swiglu_impl(plan, x_sorted, false, W1_ND2H, h_sorted, a_out, b_out, ab_mode, stream, x_MD, tile_ready);
 }
 
 MOMOE_API int momoe_up_swiglu_tokens(const momoe_plan_t* plan, const void* x_MD, const void* W1_ND2H, void* h_sorted,

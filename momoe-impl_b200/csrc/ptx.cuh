@@ -60,34 +60,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// Bounded wait until the int at `p` (written by other thread blocks with red_release_add) is at least `want`.
-__device__ __forceinline__ bool flag_wait_ge(const int* p, int want, volatile int* abort_flag, int* status, int code) {
-    const long long t0 = clock64();
-    for (uint32_t spin = 1;; ++spin) {
-        int v;
-        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-        if (v >= want) return true;
-        if ((spin & 0x3F) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-        __nanosleep(64);
-    }
-}
-// Publishes everything this warp wrote before the preceding __syncwarp(): release increment at device scope.
-__device__ __forceinline__ void red_release_add(int* p, int v) {
-    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// Orders memory written through the generic proxy (by any thread whose writes this thread has acquired) before
-// later accesses of the async proxy (TMA) issued by this thread.
-__device__ __forceinline__ void fence_proxy_async_all() {
-    asm volatile("fence.proxy.async;" ::: "memory");
-}
-
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

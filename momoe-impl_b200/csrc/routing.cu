@@ -720,14 +720,14 @@ extern "C" __attribute__((visibility("default"))) int momoe_build_permutation(co
     return LAUNCH_OK();
 }
 
-static int gather_rows_impl(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
-                            int32_t max_blocks, momoe_stream_t stream) {
+extern "C" __attribute__((visibility("default"))) int momoe_gather_rows(const momoe_plan_t* plan, const void* src, int32_t cols, void* dst_sorted,
+                                 momoe_stream_t stream) {
     if (plan == nullptr || src == nullptr || dst_sorted == nullptr || plan->row_token == nullptr ||
         plan->sched == nullptr)
         return MOMOE_ERR_ARG;
     if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
     if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_sorted)) & 15) != 0) return MOMOE_ERR_ARG;
-    const int blocks = max_blocks > 0 ? max_blocks : sm_count() * 8;
+    const int blocks = sm_count() * 8;
     // 256-bit moves need every row to start on a 32-byte boundary
     const bool wide = (cols % 16 == 0) &&
                       (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_sorted)) & 31) == 0);
@@ -741,29 +741,15 @@ static int gather_rows_impl(const momoe_plan_t* plan, const void* src, int32_t c
     return LAUNCH_OK();
 }
 
-extern "C" __attribute__((visibility("default"))) int momoe_gather_rows(const momoe_plan_t* plan, const void* src,
-                                                                       int32_t cols, void* dst_sorted,
-                                                                       momoe_stream_t stream) {
-    return gather_rows_impl(plan, src, cols, dst_sorted, 0, stream);
-}
-
-extern "C" __attribute__((visibility("default"))) int momoe_gather_rows_beside(const momoe_plan_t* plan, const void* src,
-                                                                              int32_t cols, void* dst_sorted,
-                                                                              int32_t max_blocks,
-                                                                              momoe_stream_t stream) {
-    if (max_blocks <= 0) return MOMOE_ERR_ARG;
-    return gather_rows_impl(plan, src, cols, dst_sorted, max_blocks, stream);
-}
-
-static int combine_rows_impl(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
-                             int32_t max_blocks, momoe_stream_t stream) {
+extern "C" __attribute__((visibility("default"))) int momoe_combine_rows(const momoe_plan_t* plan, const void* src_sorted, int32_t cols, void* dst,
+                                  momoe_stream_t stream) {
     if (plan == nullptr || src_sorted == nullptr || dst == nullptr || plan->pos_MK == nullptr) return MOMOE_ERR_ARG;
     if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
     if (((reinterpret_cast<uintptr_t>(src_sorted) | reinterpret_cast<uintptr_t>(dst)) & 15) != 0) return MOMOE_ERR_ARG;
     const int vec = cols / 8;
     const long long total = static_cast<long long>(plan->M) * vec;
     int blocks = cdiv(total, 256);
-    const int cap = max_blocks > 0 ? max_blocks : sm_count() * 16;
+    const int cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint4* s = static_cast<const uint4*>(src_sorted);
@@ -776,20 +762,6 @@ static int combine_rows_impl(const momoe_plan_t* plan, const void* src_sorted, i
         default: combine_rows_kernel<0><<<blocks, 256, 0, st>>>(s, plan->pos_MK, plan->M, plan->K, vec, d); break;
     }
     return LAUNCH_OK();
-}
-
-extern "C" __attribute__((visibility("default"))) int momoe_combine_rows(const momoe_plan_t* plan,
-                                                                        const void* src_sorted, int32_t cols,
-                                                                        void* dst, momoe_stream_t stream) {
-    return combine_rows_impl(plan, src_sorted, cols, dst, 0, stream);
-}
-
-extern "C" __attribute__((visibility("default"))) int momoe_combine_rows_beside(const momoe_plan_t* plan,
-                                                                               const void* src_sorted, int32_t cols,
-                                                                               void* dst, int32_t max_blocks,
-                                                                               momoe_stream_t stream) {
-    if (max_blocks <= 0) return MOMOE_ERR_ARG;
-    return combine_rows_impl(plan, src_sorted, cols, dst, max_blocks, stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int momoe_scatter_gs(const momoe_plan_t* plan, const float* gs_part, int32_t n_part, float* G_s_NM,

@@ -45,10 +45,7 @@ _PROTOS = {
                                                  c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp]),
     "momoe_gather_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
     "momoe_combine_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_vp]),
-    "momoe_gather_rows_beside": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp]),
-    "momoe_combine_rows_beside": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp]),
     "momoe_up_swiglu": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
-    "momoe_up_swiglu_gather": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "momoe_up_swiglu_tokens": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp]),
     "momoe_down_scale": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),
     "momoe_up_swiglu_decode": (C.c_int, [PlanP, c_vp, c_vp, c_vp, c_vp]),

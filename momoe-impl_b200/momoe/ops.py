@@ -226,16 +226,12 @@ def combine_rows(plan, src_sorted, cols):
     return dst
 
 
-# Row gathers folded into the grouped GEMMs (TMA row-gather loads of the token-major x and upstream gradient driven by
-# the plan's row table): no expert-major copy of either is written or read.  MOMOE_B200_FUSED_GATHER=0 restores the
-# separate `momoe_gather_rows` launches in front of the GEMMs.
+# MOMOE_B200_FUSED_GATHER=1 folds the row gathers into the grouped GEMMs (TMA row-gather loads of the token-major x and
+# upstream gradient driven by the plan's row table): no expert-major copy of either is written or read, which saves
+# two [rows, D] buffers and 1.1 GB of memory traffic per step on the headline layer.  Off by default: a row-gather load
+# moves 4 rows x 128 bytes in about 75 SM cycles, four times slower than a tiled load, and the GEMMs then wait for
+# their operands (0.93 -> 2.5 ms for the up projection).
 FUSED_GATHER = os.environ.get("MOMOE_B200_FUSED_GATHER", "0") == "1"
-
-# The up/gate kernel gathers its own A operand: four extra warps per thread block copy the token rows into expert-major
-# order while the tensor cores work on tiles whose rows are already there (`momoe_up_swiglu_gather`), so the forward pass
-# and the recomputation in the backward pass have no separate `momoe_gather_rows` launch for x.  MOMOE_B200_MOVERS=0
-# restores the separate launch.
-MOVERS = os.environ.get("MOMOE_B200_MOVERS", "1") == "1"
 
 # Forward-only calls with at most this many rows per expert on average take the weight-streaming kernels
 # (momoe_up_swiglu_decode / momoe_down_scale_decode) instead of the 256-row tile kernels.
@@ -267,12 +263,6 @@ def experts_forward(plan, x_MD, W1, W2, inference=False):
     if FUSED_GATHER:
         _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu_tokens, plan.ref, ptr(x_MD), ptr(W1), ptr(h), ptr(a_save),
               ptr(b_save), mode, stream_ptr())
-    elif MOVERS:
-        x_sorted = torch.empty((plan.rows_capacity, D), **bf)
-        ready = torch.empty(plan.tile_capacity, dtype=torch.int32, device=dev)
-        _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu_gather, plan.ref, ptr(x_MD), ptr(x_sorted), ptr(ready), ptr(W1),
-              ptr(h), ptr(a_save), ptr(b_save), mode, stream_ptr())
-        del x_sorted, ready
     else:
         x_sorted = gather_rows(plan, x_MD, D)
         _call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, plan.ref, ptr(x_sorted), ptr(W1), ptr(h), ptr(a_save),
@@ -282,71 +272,25 @@ def experts_forward(plan, x_MD, W1, W2, inference=False):
     return combine_rows(plan, y_sorted, D), a_save, b_save
 
 
-# Backward pass on two streams: row movers that are bound by HBM run on a side stream, held to a couple of blocks per SM,
-# BESIDE grouped GEMMs that are bound by the tensor cores and do not depend on them:
-#   gather of the upstream gradient   ||  gather of x + recomputation of a,b
-#   combine of the input gradient     ||  the two weight-gradient GEMMs
-# MOMOE_B200_OVERLAP=0 queues everything on one stream.
-OVERLAP = os.environ.get("MOMOE_B200_OVERLAP", "1") == "1"
-BESIDE_BLOCKS_PER_SM = int(os.environ.get("MOMOE_B200_BESIDE_BLOCKS", "2"))
-_side_streams = {}
-_sm_counts = {}
-
-
-def _side_stream(dev):
-    key = torch.device(dev).index
-    if key not in _side_streams:
-        _side_streams[key] = torch.cuda.Stream(device=dev)
-        _sm_counts[key] = torch.cuda.get_device_properties(dev).multi_processor_count
-    return _side_streams[key], _sm_counts[key]
-
-
 def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=True):
     """Returns G_x bf16 [M,D], G_W1 bf16, G_W2 bf16, G_s (dense fp32 [N,M] or per-row partial sums)."""
     dev = x_MD.device
     D, H, N = plan.D, plan.H, plan.N
     bf = dict(dtype=torch.bfloat16, device=dev)
     fused = FUSED_GATHER
-    overlap = OVERLAP and not fused and not torch.cuda.is_current_stream_capturing()
-    main = torch.cuda.current_stream(dev)
-    # every buffer is allocated on the main stream, which also waits for the side stream before this function returns
-    gx_sorted = torch.empty((plan.rows_capacity, D), **bf)
-    G_x = torch.empty((plan.M, D), **bf)
     if fused:
         g_src, x_src = g_MD, x_MD            # token-major: the GEMMs fetch rows through the plan's row table
         up, dgrad2 = lib.momoe_up_swiglu_tokens, lib.momoe_dgrad2_swiglu_bwd_tokens
     else:
+        g_src = gather_rows(plan, g_MD, D)
+        x_src = gather_rows(plan, x_MD, D)
         up, dgrad2 = lib.momoe_up_swiglu, lib.momoe_dgrad2_swiglu_bwd
-        g_src = torch.empty((plan.rows_capacity, D), **bf)
-        if overlap:
-            side, sms = _side_stream(dev)
-            blocks = sms * BESIDE_BLOCKS_PER_SM
-            ev = [torch.cuda.Event() for _ in range(4)]
-            ev[0].record(main)
-            with torch.cuda.stream(side):
-                side.wait_event(ev[0])
-                _call("momoe_gather_rows (beside)", 1, lib.momoe_gather_rows_beside, plan.ref, ptr(g_MD), D,
-                      ptr(g_src), blocks, stream_ptr())
-                ev[1].record(side)
-        else:
-            _call("momoe_gather_rows", 1, lib.momoe_gather_rows, plan.ref, ptr(g_MD), D, ptr(g_src), stream_ptr())
-        movers = MOVERS and plan.recomp_tile_capacity > 0
-        x_src = torch.empty((plan.rows_capacity, D), **bf) if movers else gather_rows(plan, x_MD, D)
     a_rec = b_rec = None
     if plan.recomp_tile_capacity > 0:
         a_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
         b_rec = torch.empty((plan.recomp_tile_capacity * TILE_M, H), **bf)
-        if not fused and movers:
-            # the recomputation launch gathers x itself; x_src is complete when it has finished (the W1 gradient
-            # reads it)
-            ready = torch.empty(plan.tile_capacity, dtype=torch.int32, device=dev)
-            _call("momoe_up_swiglu (recompute)", 1, lib.momoe_up_swiglu_gather, plan.ref, ptr(x_MD), ptr(x_src),
-                  ptr(ready), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2, stream_ptr())
-        else:
-            _call("momoe_up_swiglu (recompute)", 1, up, plan.ref, ptr(x_src), ptr(W1), None, ptr(a_rec), ptr(b_rec),
-                  2, stream_ptr())
-    if overlap:
-        main.wait_event(ev[1])
+        _call("momoe_up_swiglu (recompute)", 1, up, plan.ref, ptr(x_src), ptr(W1), None, ptr(a_rec), ptr(b_rec), 2,
+              stream_ptr())
     n_part = 2 * ((H + 255) // 256)   # two partial sums per 256-column block (momoe_dgrad2_swiglu_bwd)
     gz = torch.empty((plan.rows_capacity, 2 * H), **bf)
     hs = torch.empty((plan.rows_capacity, H), **bf)
@@ -354,14 +298,6 @@ def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=Tru
     _call("momoe_dgrad2_swiglu_bwd", 1, dgrad2, plan.ref, ptr(g_src), ptr(W2), ptr(a_save), ptr(b_save), ptr(a_rec),
           ptr(b_rec), ptr(gz), ptr(hs), ptr(gs_part), stream_ptr())
     del a_rec, b_rec
-    _call("momoe_dgrad1", 1, lib.momoe_dgrad1, plan.ref, ptr(gz), ptr(W1), ptr(gx_sorted), stream_ptr())
-    if overlap:
-        ev[2].record(main)
-        with torch.cuda.stream(side):
-            side.wait_event(ev[2])
-            _call("momoe_combine_rows (beside)", 1, lib.momoe_combine_rows_beside, plan.ref, ptr(gx_sorted), D,
-                  ptr(G_x), blocks, stream_ptr())
-            ev[3].record(side)
     G_W2 = torch.empty_like(W2)
     G_W1 = torch.empty_like(W1)
     if fused:
@@ -369,13 +305,14 @@ def experts_backward(plan, g_MD, x_MD, W1, W2, a_save, b_save, need_gs_dense=Tru
               stream_ptr())
         _call("momoe_wgrad (W1)", 1, lib.momoe_wgrad_tokens, plan.ref, ptr(x_src), D, 1, ptr(gz), 2 * H, 0, ptr(G_W1),
               stream_ptr())
+        del hs
+        gx_sorted = torch.empty((plan.rows_capacity, D), **bf)
     else:
         _call("momoe_wgrad (W2)", 1, lib.momoe_wgrad, plan.ref, ptr(hs), H, ptr(g_src), D, ptr(G_W2), stream_ptr())
         _call("momoe_wgrad (W1)", 1, lib.momoe_wgrad, plan.ref, ptr(x_src), D, ptr(gz), 2 * H, ptr(G_W1), stream_ptr())
-    if overlap:
-        main.wait_event(ev[3])
-    else:
-        _call("momoe_combine_rows", 1, lib.momoe_combine_rows, plan.ref, ptr(gx_sorted), D, ptr(G_x), stream_ptr())
+        gx_sorted = g_src  # the gathered upstream gradient is dead after the W2 gradient; reuse its buffer
+    _call("momoe_dgrad1", 1, lib.momoe_dgrad1, plan.ref, ptr(gz), ptr(W1), ptr(gx_sorted), stream_ptr())
+    G_x = combine_rows(plan, gx_sorted, D)
     if need_gs_dense:
         G_s = torch.empty((N, plan.M), dtype=torch.float32, device=dev)
         _call("momoe_scatter_gs", 1, lib.momoe_scatter_gs, plan.ref, ptr(gs_part), n_part, ptr(G_s), stream_ptr())

@@ -290,86 +290,16 @@ def test_token_major_entry_points_match_expert_major(ops, M, N, K, D, H, skew, s
     assert float(out[True]["gz"][~real].float().abs().sum()) == 0.0
     assert float(out[True]["hs"][~real].float().abs().sum()) == 0.0
     # and the layer through the public sequences, both settings of the switch
-    # (fused gathers; separate gathers on one stream; separate gathers with the movers beside the GEMMs on a second
-    # stream): identical bits
-    res = []
-    keep = (ops.FUSED_GATHER, ops.OVERLAP)
-    for fused, overlap in ((True, False), (False, False), (False, True)):
-        ops.FUSED_GATHER, ops.OVERLAP = fused, overlap
+    res = {}
+    keep = ops.FUSED_GATHER
+    for fused in (True, False):
+        ops.FUSED_GATHER = fused
         try:
             y, a_save, b_save = ops.experts_forward(plan, x, W1, W2)
-            res.append((y,) + tuple(ops.experts_backward(plan, gy, x, W1, W2, a_save, b_save, need_gs_dense=True)))
+            res[fused] = (y,) + tuple(ops.experts_backward(plan, gy, x, W1, W2, a_save, b_save, need_gs_dense=True))
         finally:
-            ops.FUSED_GATHER, ops.OVERLAP = keep
+            ops.FUSED_GATHER = keep
     torch.cuda.synchronize()
     ops.check_status()
-    for other in res[1:]:
-        for a, b in zip(res[0], other):
-            assert torch.equal(a, b)
-
-
-@pytest.mark.parametrize("M,N,K,D,H,skew", SHAPES + [(4096, 32, 8, 2048, 1024, 1.0), (16, 64, 2, 128, 64, 0.0)])
-@pytest.mark.parametrize("save_percent", [0, 50])
-def test_up_swiglu_gathering_its_own_rows(ops, M, N, K, D, H, skew, save_percent):
-    """`momoe_up_swiglu_gather` (four extra warps per thread block copy the token rows into expert-major order while
-    the tiles run; the TMA producer waits for a tile's 128 rows) against `momoe_gather_rows` + `momoe_up_swiglu`: the
-    expert-major copy byte for byte, h / a / b bit for bit, for the forward form and the recomputation form.  The last
-    shape has far fewer work items than thread blocks: blocks without tiles still move rows."""
-    _lib = lib_of(ops)
-    L = _lib.lib
-    ptr, st = _lib.ptr, _lib.stream_ptr
-    plan, x, W1, W2, pad = _setup(ops, M, N, K, D, H, skew, save_percent)
-    rows = pad[-1]
-    bf = dict(dtype=torch.bfloat16, device="cuda")
-    nan = float("nan")
-    xs = ops.gather_rows(plan, x, D)
-    mode = 1 if plan.saved_tile_capacity > 0 else 0
-    out = {}
-    for movers in (False, True):
-        h = torch.full((plan.rows_capacity, H), nan, **bf)
-        a_s = b_s = None
-        if mode:
-            a_s = torch.full((plan.saved_tile_capacity * 128, H), nan, **bf)
-            b_s = torch.full((plan.saved_tile_capacity * 128, H), nan, **bf)
-        a_r = torch.full((plan.recomp_tile_capacity * 128, H), nan, **bf)
-        b_r = torch.full((plan.recomp_tile_capacity * 128, H), nan, **bf)
-        if movers:
-            xs1 = torch.full((plan.rows_capacity, D), nan, **bf)
-            xs2 = torch.full((plan.rows_capacity, D), nan, **bf)
-            ready = torch.full((plan.tile_capacity,), 77, dtype=torch.int32, device="cuda")   # the call zeroes it
-            _lib.check(L.momoe_up_swiglu_gather(plan.ref, ptr(x), ptr(xs1), ptr(ready), ptr(W1), ptr(h), ptr(a_s),
-                                                ptr(b_s), mode, st()), "up gather")
-            _lib.check(L.momoe_up_swiglu_gather(plan.ref, ptr(x), ptr(xs2), ptr(ready), ptr(W1), None, ptr(a_r),
-                                                ptr(b_r), 2, st()), "up gather recompute")
-            torch.cuda.synchronize()
-            ops.check_status()
-            assert torch.equal(xs1[:rows], xs[:rows]) and torch.equal(xs2[:rows], xs[:rows])
-            n_tiles = int(plan.sched[0])
-            assert torch.all(ready[:n_tiles] == 128)
-        else:
-            _lib.check(L.momoe_up_swiglu(plan.ref, ptr(xs), ptr(W1), ptr(h), ptr(a_s), ptr(b_s), mode, st()), "up")
-            _lib.check(L.momoe_up_swiglu(plan.ref, ptr(xs), ptr(W1), None, ptr(a_r), ptr(b_r), 2, st()), "up rec")
-            torch.cuda.synchronize()
-            ops.check_status()
-        n_saved, n_tiles = int(plan.sched[1]), int(plan.sched[0])
-        out[movers] = [h[:rows], a_r[:(n_tiles - n_saved) * 128], b_r[:(n_tiles - n_saved) * 128]]
-        if mode:
-            out[movers] += [a_s[:n_saved * 128], b_s[:n_saved * 128]]
-    for a, b in zip(out[False], out[True]):
-        assert torch.isfinite(b.float()).all()
-        assert torch.equal(a, b)
-    # and the layer's public sequences with and without the in-kernel gather: identical bits
-    gy = torch.randn(M, D, generator=torch.Generator().manual_seed(9)).bfloat16().cuda()
-    res = []
-    keep = ops.MOVERS
-    for movers in (True, False):
-        ops.MOVERS = movers
-        try:
-            y, a_save, b_save = ops.experts_forward(plan, x, W1, W2)
-            res.append((y,) + tuple(ops.experts_backward(plan, gy, x, W1, W2, a_save, b_save, need_gs_dense=True)))
-        finally:
-            ops.MOVERS = keep
-    torch.cuda.synchronize()
-    ops.check_status()
-    for a, b in zip(res[0], res[1]):
+    for a, b in zip(res[True], res[False]):
         assert torch.equal(a, b)

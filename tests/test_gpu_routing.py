@@ -191,25 +191,3 @@ def test_gather_rows_from_a_row_table_only(ops, M, n_rows, D):
     for k in range(K):
         acc += ref[:, k]
     assert torch.equal(y, acc.bfloat16())
-
-
-def test_row_movers_with_a_block_limit_match(ops):
-    """`momoe_gather_rows_beside` / `momoe_combine_rows_beside` (grid held to a few blocks so that the mover can run
-    beside a grouped GEMM) move exactly what the plain entry points move."""
-    from momoe import _lib
-    L, ptr, st = _lib.lib, _lib.ptr, _lib.stream_ptr
-    M, N, K, D = 3000, 16, 4, 1024
-    topk_idx, topk_w = make_routing(M, N, K, seed=5, skew=1.0)
-    plan = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, 64)
-    x = torch.randn(M, D, generator=torch.Generator().manual_seed(2)).bfloat16().cuda()
-    xs = ops.gather_rows(plan, x, D)
-    y = ops.combine_rows(plan, xs, D)
-    for blocks in (1, 148, 296):
-        xs2 = torch.full_like(xs, float("nan"))
-        y2 = torch.full_like(y, float("nan"))
-        _lib.check(L.momoe_gather_rows_beside(plan.ref, ptr(x), D, ptr(xs2), blocks, st()), "gather beside")
-        _lib.check(L.momoe_combine_rows_beside(plan.ref, ptr(xs2), D, ptr(y2), blocks, st()), "combine beside")
-        torch.cuda.synchronize()
-        rows = int(plan.sched[2])
-        assert torch.equal(xs2[:rows], xs[:rows]) and torch.equal(y2, y)
-    assert L.momoe_gather_rows_beside(plan.ref, ptr(x), D, ptr(xs), 0, st()) == -1
