@@ -49,6 +49,10 @@ class ClockSampler:
 
     def __init__(self, index):
         self.proc = None
+        # nvidia-smi numbers the box's GPUs; CUDA's device `index` counts inside CUDA_VISIBLE_DEVICES when that is set
+        visible = [v.strip() for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+        if index < len(visible):
+            index = visible[index]
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
                                           "--format=csv,noheader,nounits", "-lms", "100"],
