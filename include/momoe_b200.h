@@ -250,6 +250,18 @@ int momoe_ep_plan(const int32_t* counts_RN, int32_t world, int32_t rank, int32_t
                   int32_t* pad_off, int32_t* tile_expert, int32_t* pair_info, int32_t* sched, int32_t* status,
                   momoe_stream_t stream);
 
+/* momoe_ep_plan that also cuts this rank's expert block in two parts, local experts [0, split_expert) and
+ * [split_expert, N/R), so that the transfers of one part can run while the grouped GEMMs work on the other:
+ * pair_info_parts int32[2 * (cap_rows/128)] receives the pair table of part 0 at [0] and of part 1 at
+ * [cap_rows/128], sched_parts int32[2*8] the matching schedule words (sched_parts[8*p + 3] = pairs of part p; tile
+ * numbers, and with them the boundary of the saved tiles, are those of the whole block).  A momoe_plan_t that points
+ * at one part's tables makes the row-tile GEMMs (up, down, dgrad-2, dgrad-1) work on that part's experts only. */
+int momoe_ep_plan_split(const int32_t* counts_RN, int32_t world, int32_t rank, int32_t N, double save_percent,
+                        int64_t cap_rows, int32_t* dst_base_N, int64_t* sizes_global_N, int32_t* local_count,
+                        int32_t* pad_off, int32_t* tile_expert, int32_t* pair_info, int32_t* sched,
+                        int32_t split_expert, int32_t* pair_info_parts, int32_t* sched_parts, int32_t* status,
+                        momoe_stream_t stream);
+
 /* Gather + send: row src[token,:] of every (token, expert) pair of `home` (this rank's own permutation over all N
  * experts) is stored into the owner's expert-major buffer at dst_base_N[e] + (index among this rank's tokens of e);
  * peer_row_weight (may be NULL) receives the routing weight, remote_row (may be NULL, int32[home rows_capacity])
@@ -262,10 +274,33 @@ int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int32_t co
                            int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
                            const int32_t* local_pad_off, int32_t max_blocks, momoe_stream_t stream);
 
+/* momoe_ep_dispatch_rows for the (token, expert) pairs whose expert is one of its owner's local experts
+ * [expert_lo, expert_hi) only (and the padding rows of this rank's own experts in that range). */
+int momoe_ep_dispatch_rows_range(const momoe_plan_t* home, const void* src, int32_t cols, const int32_t* dst_base_N,
+                                 int32_t experts_per_rank, void* const* peer_rows, void* const* peer_row_weight,
+                                 int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
+                                 const int32_t* local_pad_off, int32_t expert_lo, int32_t expert_hi,
+                                 int32_t max_blocks, momoe_stream_t stream);
+
+/* Receive without reducing: the result rows of this rank's (token, expert) pairs whose expert is one of its owner's
+ * local experts [expert_lo, expert_hi) are copied from the owners into staged_rows (bf16 [home rows_capacity, cols],
+ * local memory, row index = the pair's row in `home`).  Queued beside the GEMMs of the other experts. */
+int momoe_ep_pull_rows(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
+                       int32_t experts_per_rank, int32_t cols, void* staged_rows, int32_t world, int32_t rank,
+                       int32_t expert_lo, int32_t expert_hi, int32_t max_blocks, momoe_stream_t stream);
+
 /* Receive + reduce: dst[m,:] = bf16(sum_k rows@owner(m,k)[remote_row,:]), fp32 accumulation in ascending k. */
 int momoe_ep_combine_rows(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
                           int32_t experts_per_rank, int32_t cols, void* dst, int32_t world, int32_t max_blocks,
                           momoe_stream_t stream);
+
+/* momoe_ep_combine_rows where the rows of the owners' local experts [expert_lo, expert_hi) were fetched before by
+ * momoe_ep_pull_rows and are read from staged_rows; the other rows come from their owners.  Same summation order,
+ * so the result is identical bit for bit to momoe_ep_combine_rows. */
+int momoe_ep_combine_rows_staged(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
+                                 int32_t experts_per_rank, int32_t cols, void* dst, int32_t world,
+                                 const void* staged_rows, int32_t expert_lo, int32_t expert_hi, int32_t max_blocks,
+                                 momoe_stream_t stream);
 
 /* row_gs[r] = sum of the dgrad-2 partial sums of local row r. */
 int momoe_ep_reduce_gs(const float* gs_part, int32_t n_part, const int32_t* sched, float* row_gs,

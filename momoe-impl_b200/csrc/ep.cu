@@ -85,7 +85,8 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_RN, int world, int
                                long long cap_rows, int tile_capacity, int* __restrict__ dst_base,
                                long long* __restrict__ sizes_global, int* __restrict__ local_count,
                                int* __restrict__ pad_off, int* __restrict__ tile_expert, int* __restrict__ pair_info,
-                               int* __restrict__ sched, int* status) {
+                               int* __restrict__ sched, int* status, int split, int* __restrict__ pair_info_part,
+                               int* __restrict__ sched_part) {
     __shared__ int s_tot[1024];       // tokens per global expert, all sources
     __shared__ int s_before[1024];    // of those, from ranks below mine
     __shared__ int s_padoff[1024];    // first padded row of the expert inside its owner's layout
@@ -133,6 +134,7 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_RN, int world, int
     if (e == 0) {
         // serial pass over the local block: pair table, unpadded prefix for the save rule
         int pairs = 0, unpadded = 0, total = 0;
+        int part_pairs[2] = {0, 0}, part_rows[2] = {0, 0};
         for (int el = 0; el < Nl; ++el) total += over ? 0 : s_tot[rank * Nl + el];
         const long long save_rows = static_cast<long long>(static_cast<double>(total) * save_percent / 100.0);
         int saved = 0;
@@ -140,8 +142,16 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_RN, int world, int
             const int cnt = over ? 0 : s_tot[rank * Nl + el];
             const int ntile = (cnt + TILE_M - 1) / TILE_M;
             const int t0 = (over ? 0 : s_padoff[rank * Nl + el]) / TILE_M;
-            for (int j = 0; 2 * j < ntile && pairs < tile_capacity; ++j)
-                pair_info[pairs++] = (t0 + 2 * j) * 2 + (2 * j + 1 < ntile ? 1 : 0);
+            for (int j = 0; 2 * j < ntile && pairs < tile_capacity; ++j) {
+                const int info = (t0 + 2 * j) * 2 + (2 * j + 1 < ntile ? 1 : 0);
+                pair_info[pairs++] = info;
+                if (pair_info_part != nullptr) {
+                    // the same pair again in the table of its part: local experts below `split`, and the rest
+                    const int part = el < split ? 0 : 1;
+                    pair_info_part[part * tile_capacity + part_pairs[part]++] = info;
+                }
+            }
+            part_rows[el < split ? 0 : 1] += ntile * TILE_M;
             long long fit = (save_rows - unpadded) / TILE_M;
             if (fit < 0) fit = 0;
             if (fit > ntile) fit = ntile;
@@ -155,6 +165,17 @@ __global__ void ep_plan_kernel(const int* __restrict__ counts_RN, int world, int
         sched[SCHED_PAD_ROWS] = rows;
         sched[SCHED_N_PAIRS] = pairs;
         for (int i = 4; i < SCHED_WORDS; ++i) sched[i] = 0;
+        if (sched_part != nullptr) {
+            // tile numbers stay those of the whole block, so the boundary of the saved tiles is the same number
+            for (int part = 0; part < 2; ++part) {
+                int* sp = sched_part + part * SCHED_WORDS;
+                for (int i = 0; i < SCHED_WORDS; ++i) sp[i] = 0;
+                sp[SCHED_N_TILES] = rows / TILE_M;
+                sp[SCHED_N_SAVED_TILES] = saved;
+                sp[SCHED_PAD_ROWS] = part_rows[part];
+                sp[SCHED_N_PAIRS] = part_pairs[part];
+            }
+        }
     }
 }
 
@@ -177,15 +198,18 @@ ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ h
                         const float* __restrict__ home_row_weight, const int* __restrict__ dst_base, int Nl,
                         int vec_per_row, PeerPtrs rows, PeerPtrs row_w, int* __restrict__ remote_row, int rank,
                         int world, const int* __restrict__ local_count, const int* __restrict__ local_pad_off,
-                        bool wide, const int* __restrict__ status) {
+                        bool wide, const int* __restrict__ status, int e_lo, int e_hi) {
     // a hand-shake that timed out leaves counts and plans that cannot be trusted: no payload is sent then; like an
     // overflow (302, dst_base = -1) the rows still get an in-range remote_row so that later reads stay inside the buffers
     const bool no_send = status != nullptr && *reinterpret_cast<const volatile int*>(status) == DEV_TIMEOUT_PEER;
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (blockDim.x >> 5);
     const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    int max_len = 0;   // longest of the per-destination segments of my expert-major rows
-    for (int d = 0; d < world; ++d) max_len = max(max_len, home_pad_off[(d + 1) * Nl] - home_pad_off[d * Nl]);
+    // Only rows of the owners' local experts [e_lo, e_hi) are sent: for one destination these are one contiguous run
+    // of my expert-major rows.
+    int max_len = 0;   // longest of the per-destination runs
+    for (int d = 0; d < world; ++d)
+        max_len = max(max_len, home_pad_off[d * Nl + e_hi] - home_pad_off[d * Nl + e_lo]);
     const long long n_slots = static_cast<long long>(max_len) * world;
     // a warp changes its destination from one row to the next (a bijection while the warp count is a multiple of the
     // rank count), so that no warp only ever serves the fast local copies
@@ -196,8 +220,8 @@ ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ h
         if (rotate) d = static_cast<int>((d + j / warps_total) % world);
         d += rank + 1;
         if (d >= world) d -= world;
-        const int lo = home_pad_off[d * Nl];
-        if (off >= home_pad_off[(d + 1) * Nl] - lo) continue;
+        const int lo = home_pad_off[d * Nl + e_lo];
+        if (off >= home_pad_off[d * Nl + e_hi] - lo) continue;
         const int pr = lo + off;
         const int tok = home_row_token[pr];
         if (tok < 0) continue;
@@ -235,7 +259,7 @@ ep_dispatch_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ h
     // padding rows of my own receive buffer
     uint4* mine = static_cast<uint4*>(rows.p[rank]);
     float* mine_w = row_w.p[0] != nullptr ? static_cast<float*>(row_w.p[rank]) : nullptr;
-    for (int el = 0; el < Nl; ++el) {
+    for (int el = e_lo; el < e_hi; ++el) {
         const int lo = local_pad_off[el] + local_count[el];
         const int hi = local_pad_off[el + 1];
         for (int r = lo + wid; r < hi; r += warps_total) {
@@ -300,6 +324,88 @@ __global__ void ep_combine_rows_generic_kernel(PeerPtrs rows, const int* __restr
             const int pr = home_pos[static_cast<size_t>(m) * K + k];
             const int d = home_tile_expert[pr / TILE_M] / Nl;
             acc8(ld_peer(static_cast<const uint4*>(rows.p[d]) + static_cast<size_t>(remote_row[pr]) * vec_per_row + c), a);
+        }
+        dst[i] = make_uint4(pk(a[0], a[1]), pk(a[2], a[3]), pk(a[4], a[5]), pk(a[6], a[7]));
+    }
+}
+
+// Receive only: the result rows of this rank's (token, expert) pairs whose expert is one of the owners' local experts
+// [e_lo, e_hi) are copied from their owners into `staged`, a local buffer indexed like this rank's own expert-major
+// order (row pr of `home`).  One warp per row, destinations visited round-robin as in the dispatch.  The sum over a
+// token's K rows is left to momoe_ep_combine_rows_staged, which reads these rows from local memory, so the order of
+// the fp32 summation does not depend on how the transfer was split.
+__global__ void __launch_bounds__(256, 4)
+ep_pull_rows_kernel(PeerPtrs rows, const int* __restrict__ home_row_token, const int* __restrict__ home_pad_off,
+                    const int* __restrict__ remote_row, int Nl, int vec_per_row, uint4* __restrict__ staged, int rank,
+                    int world, int e_lo, int e_hi) {
+    const int lane = threadIdx.x & 31;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int max_len = 0;
+    for (int d = 0; d < world; ++d)
+        max_len = max(max_len, home_pad_off[d * Nl + e_hi] - home_pad_off[d * Nl + e_lo]);
+    const long long n_slots = static_cast<long long>(max_len) * world;
+    const bool rotate = warps_total % world == 0;
+    for (long long j = wid; j < n_slots; j += warps_total) {
+        const int off = static_cast<int>(j / world);
+        int d = static_cast<int>(j - static_cast<long long>(off) * world);
+        if (rotate) d = static_cast<int>((d + j / warps_total) % world);
+        d += rank + 1;
+        if (d >= world) d -= world;
+        const int lo = home_pad_off[d * Nl + e_lo];
+        if (off >= home_pad_off[d * Nl + e_hi] - lo) continue;
+        const int pr = lo + off;
+        if (home_row_token[pr] < 0) continue;
+        const uint4* s = static_cast<const uint4*>(rows.p[d]) + static_cast<size_t>(remote_row[pr]) * vec_per_row;
+        uint4* dst = staged + static_cast<size_t>(pr) * vec_per_row;
+        for (int c0 = lane; c0 < vec_per_row; c0 += 128) {
+            uint4 t[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (c0 + i * 32 < vec_per_row) t[i] = ld_peer(s + c0 + i * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (c0 + i * 32 < vec_per_row) dst[c0 + i * 32] = t[i];
+        }
+    }
+}
+
+// momoe_ep_combine_rows with part of the rows already local: a row whose expert is one of its owner's local experts
+// [e_lo, e_hi) is read from `staged` (row pr), every other row from its owner.  Same fp32 summation in ascending k.
+template <int KT>
+__global__ void ep_combine_rows_staged_kernel(PeerPtrs rows, const int* __restrict__ home_pos,
+                                              const int* __restrict__ home_tile_expert,
+                                              const int* __restrict__ remote_row, int Nl, int M, int K, int vec_per_row,
+                                              uint4* __restrict__ dst, const uint4* __restrict__ staged, int e_lo,
+                                              int e_hi) {
+    const long long total = static_cast<long long>(M) * vec_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int m = static_cast<int>(i / vec_per_row);
+        const int c = static_cast<int>(i - static_cast<long long>(m) * vec_per_row);
+        float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (KT > 0) {
+            uint4 q[KT > 0 ? KT : 1];
+#pragma unroll
+            for (int k = 0; k < KT; ++k) {
+                const int pr = home_pos[static_cast<size_t>(m) * KT + k];
+                const int e = home_tile_expert[pr / TILE_M];
+                const int d = e / Nl;
+                const int le = e - d * Nl;
+                if (le >= e_lo && le < e_hi) q[k] = staged[static_cast<size_t>(pr) * vec_per_row + c];
+                else q[k] = ld_peer(static_cast<const uint4*>(rows.p[d]) + static_cast<size_t>(remote_row[pr]) * vec_per_row + c);
+            }
+#pragma unroll
+            for (int k = 0; k < KT; ++k) acc8(q[k], a);
+        } else {
+            for (int k = 0; k < K; ++k) {
+                const int pr = home_pos[static_cast<size_t>(m) * K + k];
+                const int e = home_tile_expert[pr / TILE_M];
+                const int d = e / Nl;
+                const int le = e - d * Nl;
+                if (le >= e_lo && le < e_hi) acc8(staged[static_cast<size_t>(pr) * vec_per_row + c], a);
+                else acc8(ld_peer(static_cast<const uint4*>(rows.p[d]) + static_cast<size_t>(remote_row[pr]) * vec_per_row + c), a);
+            }
         }
         dst[i] = make_uint4(pk(a[0], a[1]), pk(a[2], a[3]), pk(a[4], a[5]), pk(a[6], a[7]));
     }
@@ -393,20 +499,44 @@ EP_API int momoe_ep_plan(const int32_t* counts_RN, int32_t world, int32_t rank, 
         return MOMOE_ERR_ARG;
     ep_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
         counts_RN, world, rank, N, save_percent, cap_rows, static_cast<int>(cap_rows / TILE_M), dst_base_N,
-        reinterpret_cast<long long*>(sizes_global_N), local_count, pad_off, tile_expert, pair_info, sched, status);
+        reinterpret_cast<long long*>(sizes_global_N), local_count, pad_off, tile_expert, pair_info, sched, status, 0,
+        nullptr, nullptr);
     return EP_LAUNCH_OK();
 }
 
-EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int32_t cols, const int32_t* dst_base_N,
-                                  int32_t experts_per_rank, void* const* peer_rows, void* const* peer_row_weight,
-                                  int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
-                                  const int32_t* local_pad_off, int32_t max_blocks, momoe_stream_t stream) {
+EP_API int momoe_ep_plan_split(const int32_t* counts_RN, int32_t world, int32_t rank, int32_t N, double save_percent,
+                               int64_t cap_rows, int32_t* dst_base_N, int64_t* sizes_global_N, int32_t* local_count,
+                               int32_t* pad_off, int32_t* tile_expert, int32_t* pair_info, int32_t* sched,
+                               int32_t split_expert, int32_t* pair_info_parts, int32_t* sched_parts, int32_t* status,
+                               momoe_stream_t stream) {
+    if (counts_RN == nullptr || dst_base_N == nullptr || sizes_global_N == nullptr || local_count == nullptr ||
+        pad_off == nullptr || tile_expert == nullptr || pair_info == nullptr || sched == nullptr || status == nullptr ||
+        pair_info_parts == nullptr || sched_parts == nullptr)
+        return MOMOE_ERR_ARG;
+    if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world || N <= 0 || N > 1024 || N % world != 0)
+        return MOMOE_ERR_ARG;
+    if (cap_rows <= 0 || cap_rows % TILE_M != 0 || cap_rows > 0x7fffffffLL || save_percent < 0 || save_percent > 100)
+        return MOMOE_ERR_ARG;
+    if (split_expert < 0 || split_expert > N / world) return MOMOE_ERR_ARG;
+    ep_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+        counts_RN, world, rank, N, save_percent, cap_rows, static_cast<int>(cap_rows / TILE_M), dst_base_N,
+        reinterpret_cast<long long*>(sizes_global_N), local_count, pad_off, tile_expert, pair_info, sched, status,
+        split_expert, pair_info_parts, sched_parts);
+    return EP_LAUNCH_OK();
+}
+
+static int dispatch_rows_impl(const momoe_plan_t* home, const void* src, int32_t cols, const int32_t* dst_base_N,
+                              int32_t experts_per_rank, void* const* peer_rows, void* const* peer_row_weight,
+                              int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
+                              const int32_t* local_pad_off, int32_t e_lo, int32_t e_hi, int32_t max_blocks,
+                              momoe_stream_t stream) {
     if (home == nullptr || src == nullptr || dst_base_N == nullptr || peer_rows == nullptr || local_count == nullptr ||
         local_pad_off == nullptr || home->row_token == nullptr || home->tile_expert == nullptr ||
         home->pad_off == nullptr || home->sched == nullptr || home->row_weight == nullptr)
         return MOMOE_ERR_ARG;
     if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
     if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world || experts_per_rank <= 0) return MOMOE_ERR_ARG;
+    if (e_lo < 0 || e_hi > experts_per_rank || e_lo > e_hi) return MOMOE_ERR_ARG;
     PeerPtrs r, w;
     if (fill_peers(r, peer_rows, world) != MOMOE_OK || fill_peers(w, peer_row_weight, world) != MOMOE_OK)
         return MOMOE_ERR_ARG;
@@ -417,7 +547,77 @@ EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int
     ep_dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(src), home->row_token, home->tile_expert, home->pad_off, home->row_weight,
         dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, world, local_count, local_pad_off, wide,
-        home->status);
+        home->status, e_lo, e_hi);
+    return EP_LAUNCH_OK();
+}
+
+EP_API int momoe_ep_dispatch_rows(const momoe_plan_t* home, const void* src, int32_t cols, const int32_t* dst_base_N,
+                                  int32_t experts_per_rank, void* const* peer_rows, void* const* peer_row_weight,
+                                  int32_t* remote_row, int32_t world, int32_t rank, const int32_t* local_count,
+                                  const int32_t* local_pad_off, int32_t max_blocks, momoe_stream_t stream) {
+    return dispatch_rows_impl(home, src, cols, dst_base_N, experts_per_rank, peer_rows, peer_row_weight, remote_row,
+                              world, rank, local_count, local_pad_off, 0, experts_per_rank, max_blocks, stream);
+}
+
+EP_API int momoe_ep_dispatch_rows_range(const momoe_plan_t* home, const void* src, int32_t cols,
+                                        const int32_t* dst_base_N, int32_t experts_per_rank, void* const* peer_rows,
+                                        void* const* peer_row_weight, int32_t* remote_row, int32_t world, int32_t rank,
+                                        const int32_t* local_count, const int32_t* local_pad_off, int32_t expert_lo,
+                                        int32_t expert_hi, int32_t max_blocks, momoe_stream_t stream) {
+    return dispatch_rows_impl(home, src, cols, dst_base_N, experts_per_rank, peer_rows, peer_row_weight, remote_row,
+                              world, rank, local_count, local_pad_off, expert_lo, expert_hi, max_blocks, stream);
+}
+
+EP_API int momoe_ep_pull_rows(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
+                              int32_t experts_per_rank, int32_t cols, void* staged_rows, int32_t world, int32_t rank,
+                              int32_t expert_lo, int32_t expert_hi, int32_t max_blocks, momoe_stream_t stream) {
+    if (home == nullptr || peer_rows == nullptr || remote_row == nullptr || staged_rows == nullptr ||
+        home->row_token == nullptr || home->pad_off == nullptr)
+        return MOMOE_ERR_ARG;
+    if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
+    if (world < 1 || world > EP_MAX_RANKS || rank < 0 || rank >= world || experts_per_rank <= 0) return MOMOE_ERR_ARG;
+    if (expert_lo < 0 || expert_hi > experts_per_rank || expert_lo > expert_hi) return MOMOE_ERR_ARG;
+    PeerPtrs r;
+    if (fill_peers(r, peer_rows, world) != MOMOE_OK) return MOMOE_ERR_ARG;
+    const int grid = max_blocks > 0 ? max_blocks : sm_count() * 8;
+    ep_pull_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        r, home->row_token, home->pad_off, remote_row, experts_per_rank, cols / 8, static_cast<uint4*>(staged_rows),
+        rank, world, expert_lo, expert_hi);
+    return EP_LAUNCH_OK();
+}
+
+EP_API int momoe_ep_combine_rows_staged(const momoe_plan_t* home, void* const* peer_rows, const int32_t* remote_row,
+                                        int32_t experts_per_rank, int32_t cols, void* dst, int32_t world,
+                                        const void* staged_rows, int32_t expert_lo, int32_t expert_hi,
+                                        int32_t max_blocks, momoe_stream_t stream) {
+    if (home == nullptr || peer_rows == nullptr || remote_row == nullptr || dst == nullptr || home->pos_MK == nullptr ||
+        home->tile_expert == nullptr || staged_rows == nullptr)
+        return MOMOE_ERR_ARG;
+    if (cols <= 0 || cols % 8 != 0) return MOMOE_ERR_UNSUPPORTED;
+    if (world < 1 || world > EP_MAX_RANKS || experts_per_rank <= 0) return MOMOE_ERR_ARG;
+    if (expert_lo < 0 || expert_hi > experts_per_rank || expert_lo > expert_hi) return MOMOE_ERR_ARG;
+    PeerPtrs r;
+    if (fill_peers(r, peer_rows, world) != MOMOE_OK) return MOMOE_ERR_ARG;
+    const int vec = cols / 8;
+    const long long total = static_cast<long long>(home->M) * vec;
+    int blocks = static_cast<int>((total + 255) / 256);
+    const int cap = max_blocks > 0 ? max_blocks : sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint4* d = static_cast<uint4*>(dst);
+    const uint4* sg = static_cast<const uint4*>(staged_rows);
+#define MOMOE_COMBINE_STAGED(KT)                                                                                      \
+    ep_combine_rows_staged_kernel<KT><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row,         \
+                                                              experts_per_rank, home->M, home->K, vec, d, sg,         \
+                                                              expert_lo, expert_hi)
+    switch (home->K) {
+        case 2: MOMOE_COMBINE_STAGED(2); break;
+        case 4: MOMOE_COMBINE_STAGED(4); break;
+        case 6: MOMOE_COMBINE_STAGED(6); break;
+        case 8: MOMOE_COMBINE_STAGED(8); break;
+        default: MOMOE_COMBINE_STAGED(0); break;
+    }
+#undef MOMOE_COMBINE_STAGED
     return EP_LAUNCH_OK();
 }
 

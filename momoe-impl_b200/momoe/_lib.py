@@ -68,6 +68,13 @@ _PROTOS = {
     "momoe_ep_dispatch_rows": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_vp, c_vp,
                                          c_i32, c_vp]),
     "momoe_ep_combine_rows": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_i32, c_vp, c_i32, c_i32, c_vp]),
+    "momoe_ep_plan_split": (C.c_int, [c_vp, c_i32, c_i32, c_i32, C.c_double, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+                                      c_vp, c_i32, c_vp, c_vp, c_vp, c_vp]),
+    "momoe_ep_dispatch_rows_range": (C.c_int, [PlanP, c_vp, c_i32, c_vp, c_i32, c_vp, c_vp, c_vp, c_i32, c_i32, c_vp,
+                                               c_vp, c_i32, c_i32, c_i32, c_vp]),
+    "momoe_ep_pull_rows": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_i32, c_vp, c_i32, c_i32, c_i32, c_i32, c_i32, c_vp]),
+    "momoe_ep_combine_rows_staged": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_i32, c_vp, c_i32, c_vp, c_i32, c_i32, c_i32,
+                                               c_vp]),
     "momoe_ep_reduce_gs": (C.c_int, [c_vp, c_i32, c_vp, c_vp, c_vp]),
     "momoe_ep_pull_gs_compact": (C.c_int, [PlanP, c_vp, c_vp, c_i32, c_vp, c_i32, c_vp]),
 }

@@ -194,6 +194,8 @@ class PeerBuffers:
         self.epoch = 0
         self._keep = []
         self.max_tokens = 0        # tokens per rank the buffers were sized for (set by the layer)
+        self.forward_chunks = None  # 1: transfers and GEMMs of a forward pass in sequence; 2: in two overlapping halves;
+                                    # None: 2 for passes that move at least 16 MiB of rows per rank
         self._step = 0             # forward passes started
         self._pending = 0          # step whose backward pass has not run yet (0: none)
 
@@ -211,7 +213,11 @@ class PeerBuffers:
         self.row_w, self.p_row_w = alloc((cap_rows,), torch.float32)          # routing weight of each received row
         self.row_gs, self.p_row_gs = alloc((cap_rows,), torch.float32)        # dL/ds of each received row
         self.counts, self.p_counts = alloc((self.world * N,), torch.int32)
-        self.flags, self.p_flags = alloc((8,), torch.int32)
+        # Two hand-shake channels of 8 flag words each, with epoch counters of their own: hand-shakes queued on the
+        # transfer stream must not be satisfied by (or satisfy) the ones queued on the main stream in the same pass.
+        self.flags, self.p_flags = alloc((16,), torch.int32)
+        self.p_flags_b = (C.c_void_p * self.world)(*[C.c_void_p(int(p) + 32) for p in self._keep[-1].buffer_ptrs])
+        self.epoch_b = 0
         self.comm_stream = torch.cuda.Stream(device=device)
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         torch.cuda.synchronize(device)
@@ -220,6 +226,10 @@ class PeerBuffers:
     def next_epoch(self):
         self.epoch += 1
         return self.epoch
+
+    def next_epoch_b(self):
+        self.epoch_b += 1
+        return self.epoch_b
 
     # One set of buffers serves one step at a time: `rows_x` / `row_w` written by a forward pass are read again by its
     # backward pass, and `rows_y` / `rows_g` are reused by both.  A second forward pass before that backward pass
@@ -268,6 +278,13 @@ class PeerExpertParallelFunction(torch.autograd.Function):
         ctx.step = step
         ctx.step_token = _StepToken()      # dies with the autograd graph: an output dropped without backward frees the buffers
         weakref.finalize(ctx.step_token, bufs.end_step, step)
+        # Two halves of the local experts when the pass is large enough to be bound by the transfers rather than by
+        # launch latency: the rows of the second half travel while the GEMMs work on the first half, and the results
+        # of the first half travel back while the GEMMs work on the second.
+        chunks = bufs.forward_chunks
+        if chunks is None:
+            chunks = 2 if M * K * D * 2 >= (16 << 20) else 1
+        split = Nl // 2 if (chunks == 2 and Nl >= 2) else 0
         with torch.cuda.device(dev):
             home = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, H, 0.0)
             status = home.status
@@ -281,20 +298,14 @@ class PeerExpertParallelFunction(torch.autograd.Function):
             tile_expert = torch.empty(tile_cap, **i32)
             pair_info = torch.empty(tile_cap, **i32)
             sched = torch.empty(8, **i32)
-            ops._call("momoe_ep_plan", 1, lib.momoe_ep_plan, ptr(bufs.counts), R, rank, N, float(save_percent), cap,
-                      ptr(dst_base), ptr(sizes_global), ptr(local_count), ptr(pad_off), ptr(tile_expert),
-                      ptr(pair_info), ptr(sched), ptr(status), st())
-            local = _lib.Plan(M=1, N=Nl, K=1, D=D, H=H, reserved=0, rows_capacity=cap, sched=sched.data_ptr(),
-                              tile_expert=tile_expert.data_ptr(), pad_off=pad_off.data_ptr(), row_token=0,
-                              row_weight=bufs.row_w.data_ptr(), pos_MK=0, status=status.data_ptr(),
-                              pair_info=pair_info.data_ptr())
             remote_row = torch.empty(home.rows_capacity, **i32)
-            ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows, home.ref, ptr(x_MD), D, ptr(dst_base),
-                      Nl, bufs.p_rows_x, bufs.p_row_w, ptr(remote_row), R, rank, ptr(local_count), ptr(pad_off),
-                      0, st())
-            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
-                      ptr(status), st())
-            # local experts on the received rows: already expert-major and padded
+
+            def local_plan(sched_t, sched_off, pair_t, pair_off):
+                return _lib.Plan(M=1, N=Nl, K=1, D=D, H=H, reserved=0, rows_capacity=cap,
+                                 sched=sched_t.data_ptr() + 4 * sched_off, tile_expert=tile_expert.data_ptr(),
+                                 pad_off=pad_off.data_ptr(), row_token=0, row_weight=bufs.row_w.data_ptr(), pos_MK=0,
+                                 status=status.data_ptr(), pair_info=pair_t.data_ptr() + 4 * pair_off)
+
             h = torch.empty((cap, H), **bf)
             a_save = b_save = None
             mode = 0
@@ -302,18 +313,86 @@ class PeerExpertParallelFunction(torch.autograd.Function):
                 a_save = torch.empty((cap, H), **bf)
                 b_save = torch.empty((cap, H), **bf)
                 mode = 1
-            ops._call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, C.byref(local), ptr(bufs.rows_x), ptr(W1), ptr(h),
-                      ptr(a_save), ptr(b_save), mode, st())
-            ops._call("momoe_down_scale", 1, lib.momoe_down_scale, C.byref(local), ptr(h), ptr(W2), ptr(bufs.rows_y),
-                      st())
-            del h
-            ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
-                      ptr(status), st())
             y_MD = torch.empty((M, D), **bf)
-            ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y, ptr(remote_row),
-                      Nl, D, ptr(y_MD), R, 0, st())
+
+            def gemms(plan_c):
+                ops._call("momoe_up_swiglu", 1, lib.momoe_up_swiglu, C.byref(plan_c), ptr(bufs.rows_x), ptr(W1),
+                          ptr(h), ptr(a_save), ptr(b_save), mode, st())
+                ops._call("momoe_down_scale", 1, lib.momoe_down_scale, C.byref(plan_c), ptr(h), ptr(W2),
+                          ptr(bufs.rows_y), st())
+
+            if split == 0:
+                ops._call("momoe_ep_plan", 1, lib.momoe_ep_plan, ptr(bufs.counts), R, rank, N, float(save_percent),
+                          cap, ptr(dst_base), ptr(sizes_global), ptr(local_count), ptr(pad_off), ptr(tile_expert),
+                          ptr(pair_info), ptr(sched), ptr(status), st())
+                local = local_plan(sched, 0, pair_info, 0)
+                ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows, home.ref, ptr(x_MD), D,
+                          ptr(dst_base), Nl, bufs.p_rows_x, bufs.p_row_w, ptr(remote_row), R, rank, ptr(local_count),
+                          ptr(pad_off), 0, st())
+                ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                          ptr(status), st())
+                # local experts on the received rows: already expert-major and padded
+                gemms(local)
+                ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                          ptr(status), st())
+                ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows, home.ref, bufs.p_rows_y,
+                          ptr(remote_row), Nl, D, ptr(y_MD), R, 0, st())
+                parts = None
+            else:
+                pair_parts = torch.empty(2 * tile_cap, **i32)
+                sched_parts = torch.empty(16, **i32)
+                ops._call("momoe_ep_plan", 1, lib.momoe_ep_plan_split, ptr(bufs.counts), R, rank, N,
+                          float(save_percent), cap, ptr(dst_base), ptr(sizes_global), ptr(local_count), ptr(pad_off),
+                          ptr(tile_expert), ptr(pair_info), ptr(sched), split, ptr(pair_parts), ptr(sched_parts),
+                          ptr(status), st())
+                local = local_plan(sched, 0, pair_info, 0)
+                part = [local_plan(sched_parts, 0, pair_parts, 0), local_plan(sched_parts, 8, pair_parts, tile_cap)]
+                parts = (pair_parts, sched_parts)
+                main = torch.cuda.current_stream()
+                comm = bufs.comm_stream
+                one_per_sm = bufs.sm_count
+                ev = [torch.cuda.Event() for _ in range(4)]
+                staged = torch.empty((home.rows_capacity, D), **bf)
+                # rows of the first half of every rank's experts; everything else waits for them
+                ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows_range, home.ref, ptr(x_MD), D,
+                          ptr(dst_base), Nl, bufs.p_rows_x, bufs.p_row_w, ptr(remote_row), R, rank, ptr(local_count),
+                          ptr(pad_off), 0, split, 0, st())
+                ev[0].record(main)
+                ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                          ptr(status), st())
+                with torch.cuda.stream(comm):
+                    # rows of the second half beside the GEMMs of the first half
+                    comm.wait_event(ev[0])
+                    ops._call("momoe_ep_dispatch_rows", 1, lib.momoe_ep_dispatch_rows_range, home.ref, ptr(x_MD), D,
+                              ptr(dst_base), Nl, bufs.p_rows_x, bufs.p_row_w, ptr(remote_row), R, rank,
+                              ptr(local_count), ptr(pad_off), split, Nl, one_per_sm, st())
+                    ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags_b, R, rank,
+                              bufs.next_epoch_b(), ptr(status), st())
+                    ev[1].record(comm)
+                gemms(part[0])
+                ev[2].record(main)
+                with torch.cuda.stream(comm):
+                    # results of the first half come home beside the GEMMs of the second half
+                    comm.wait_event(ev[2])
+                    ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags_b, R, rank,
+                              bufs.next_epoch_b(), ptr(status), st())
+                    ops._call("momoe_ep_pull_rows", 1, lib.momoe_ep_pull_rows, home.ref, bufs.p_rows_y,
+                              ptr(remote_row), Nl, D, ptr(staged), R, rank, 0, split, one_per_sm, st())
+                    ev[3].record(comm)
+                main.wait_event(ev[1])
+                gemms(part[1])
+                ops._call("momoe_ep_barrier", 1, lib.momoe_ep_barrier, bufs.p_flags, R, rank, bufs.next_epoch(),
+                          ptr(status), st())
+                main.wait_event(ev[3])
+                ops._call("momoe_ep_combine_rows", 1, lib.momoe_ep_combine_rows_staged, home.ref, bufs.p_rows_y,
+                          ptr(remote_row), Nl, D, ptr(y_MD), R, ptr(staged), 0, split, 0, st())
+                staged.record_stream(comm)
+                x_MD.record_stream(comm)
+                del staged
+            del h
         ctx.bufs, ctx.home, ctx.local = bufs, home, local
         ctx.keep = (dst_base, local_count, pad_off, tile_expert, pair_info, sched, remote_row)
+        ctx.parts = parts      # tables the GEMMs of the two halves read: alive until the kernels have run
         ctx.shape = (B, S, D)
         ctx.dims = (N, Nl, H, K)
         ctx.save_percent = save_percent
@@ -451,6 +530,11 @@ class ExpertParallelMoE(nn.Module):
         self.transport = transport
         self.capacity_factor = capacity_factor
         self.full_checkpoints = True
+        # peer transport, forward pass: 1 = dispatch, GEMMs and combine in sequence; 2 = the local experts in two halves
+        # whose transfers overlap the other half's GEMMs (same results bit for bit); None = 2 for large passes
+        self.forward_chunks = None
+        if os.environ.get("MOMOE_B200_EP_FORWARD_CHUNKS", "") in ("1", "2"):
+            self.forward_chunks = int(os.environ["MOMOE_B200_EP_FORWARD_CHUNKS"])
         self._bufs = None
         Nl = num_experts // R
         self.router = TopKRouter(embedding_dim, num_experts, num_chosen_experts, num_shared_experts, Wg_DN=Wg_DN)
@@ -485,6 +569,7 @@ class ExpertParallelMoE(nn.Module):
             topk_idx, topk_w = CompactRouterFunction.apply(x_BSD, self.router.Wg_DN, self.biases_N, self.N, self.K,
                                                            self.Ks)
             bufs = self._peer_buffers(B * S)
+            bufs.forward_chunks = self.forward_chunks
             y_BSD, sizes_N = PeerExpertParallelFunction.apply(x_BSD, self.momoe.Wl1_ND2H, self.momoe.Wl2_NHD,
                                                               topk_idx, topk_w, self.K, self.save_percent, bufs)
         else:

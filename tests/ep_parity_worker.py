@@ -35,8 +35,11 @@ def run_case(transport, case, rank, world, dev, momoe, ep, ops, cos, max_rel):
     # load_state_dict: keys as in the reference, every rank keeps its own block of the [N, ...] expert tensors
     moe = ep.ExpertParallelMoE(D, H, N, K, Ks, save_percent=sp, bias_update_rate=1e-3,
                                Wg_DN=torch.zeros(D, N, device=dev), Wl1_ND2H=torch.zeros(Nl, D, 2 * H, device=dev),
-                               Wl2_NHD=torch.zeros(Nl, H, D, device=dev), transport=transport,
+                               Wl2_NHD=torch.zeros(Nl, H, D, device=dev), transport=transport.split("-")[0],
                                capacity_factor=float(world))   # room for any routing, however skewed
+    # "peer": transfers and GEMMs of the forward pass in sequence; "peer-halves": the local experts in two halves whose
+    # transfers overlap the other half's GEMMs (what large passes do by default)
+    moe.forward_chunks = 2 if transport == "peer-halves" else 1
     ckpt = {k: v.detach().clone() for k, v in ref.state_dict().items()}
     res = moe.load_state_dict(ckpt)
     assert not res.missing_keys and not res.unexpected_keys
@@ -83,7 +86,7 @@ def main():
         (1000, 512, 256, 16, 4, 0, 50, 0.05),
         (512, 384, 136, 8, 3, 1, 100, 0.02),
     ]
-    for transport in ("peer", "nccl"):
+    for transport in ("peer", "peer-halves", "nccl"):
         for case in cases:
             run_case(transport, case, rank, world, dev, momoe, ep, ops, cos, max_rel)
     # buffers far too small for the routing: every rank must notice (device status 302) and nothing may fault
@@ -93,6 +96,7 @@ def main():
     moe = ep.ExpertParallelMoE(D, H, N, K, 0, Wg_DN=(torch.randn(D, N, generator=g) * 0.05).bfloat16().to(dev),
                                Wl1_ND2H=torch.zeros(N // world, D, 2 * H, device=dev),
                                Wl2_NHD=torch.zeros(N // world, H, D, device=dev), capacity_factor=0.05)
+    moe.forward_chunks = 2
     x = torch.randn(1, 4096, D, generator=g).bfloat16().to(dev).requires_grad_(True)
     moe(x).sum().backward()
     torch.cuda.synchronize()
