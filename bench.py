@@ -621,7 +621,8 @@ def main():
             p.grad = None
         cur.grad = None
         y = moe(cur)
-        loss = torch.mean(torch.square(y.float()))
+        # mean-square loss: one reduction over y (fp32 accumulation) forward, one elementwise pass backward
+        loss = torch.linalg.vector_norm(y, dtype=torch.float32).square() / y.numel()
         loss.backward()
         consumed[i % 2].record(torch.cuda.current_stream())
         return float(loss.item())   # device -> host read of the step's result

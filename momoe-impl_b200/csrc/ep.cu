@@ -544,6 +544,7 @@ static int dispatch_rows_impl(const momoe_plan_t* home, const void* src, int32_t
     uintptr_t align = reinterpret_cast<uintptr_t>(src);
     for (int i = 0; i < world; ++i) align |= reinterpret_cast<uintptr_t>(r.p[i]);
     const bool wide = (cols % 16 == 0) && (align & 31) == 0;   // 256-bit stores need 32-byte aligned rows
+    share_sm_with_gemm<ep_dispatch_rows_kernel>();
     ep_dispatch_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(src), home->row_token, home->tile_expert, home->pad_off, home->row_weight,
         dst_base_N, experts_per_rank, cols / 8, r, w, remote_row, rank, world, local_count, local_pad_off, wide,
@@ -580,6 +581,7 @@ EP_API int momoe_ep_pull_rows(const momoe_plan_t* home, void* const* peer_rows, 
     PeerPtrs r;
     if (fill_peers(r, peer_rows, world) != MOMOE_OK) return MOMOE_ERR_ARG;
     const int grid = max_blocks > 0 ? max_blocks : sm_count() * 8;
+    share_sm_with_gemm<ep_pull_rows_kernel>();
     ep_pull_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         r, home->row_token, home->pad_off, remote_row, experts_per_rank, cols / 8, static_cast<uint4*>(staged_rows),
         rank, world, expert_lo, expert_hi);
@@ -607,6 +609,7 @@ EP_API int momoe_ep_combine_rows_staged(const momoe_plan_t* home, void* const* p
     uint4* d = static_cast<uint4*>(dst);
     const uint4* sg = static_cast<const uint4*>(staged_rows);
 #define MOMOE_COMBINE_STAGED(KT)                                                                                      \
+    share_sm_with_gemm<ep_combine_rows_staged_kernel<KT>>();                                                         \
     ep_combine_rows_staged_kernel<KT><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row,         \
                                                               experts_per_rank, home->M, home->K, vec, d, sg,         \
                                                               expert_lo, expert_hi)
@@ -639,11 +642,11 @@ EP_API int momoe_ep_combine_rows(const momoe_plan_t* home, void* const* peer_row
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint4* d = static_cast<uint4*>(dst);
     switch (home->K) {
-        case 2: ep_combine_rows_kernel<2><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
-        case 4: ep_combine_rows_kernel<4><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
-        case 6: ep_combine_rows_kernel<6><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
-        case 8: ep_combine_rows_kernel<8><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
-        default: ep_combine_rows_generic_kernel<<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, home->K, vec, d); break;
+        case 2: share_sm_with_gemm<ep_combine_rows_kernel<2>>(); ep_combine_rows_kernel<2><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
+        case 4: share_sm_with_gemm<ep_combine_rows_kernel<4>>(); ep_combine_rows_kernel<4><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
+        case 6: share_sm_with_gemm<ep_combine_rows_kernel<6>>(); ep_combine_rows_kernel<6><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
+        case 8: share_sm_with_gemm<ep_combine_rows_kernel<8>>(); ep_combine_rows_kernel<8><<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, vec, d); break;
+        default: share_sm_with_gemm<ep_combine_rows_generic_kernel>(); ep_combine_rows_generic_kernel<<<blocks, 256, 0, st>>>(r, home->pos_MK, home->tile_expert, remote_row, experts_per_rank, home->M, home->K, vec, d); break;
     }
     return EP_LAUNCH_OK();
 }

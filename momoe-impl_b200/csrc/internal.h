@@ -35,6 +35,22 @@ enum : int {
 enum : int { SCHED_N_TILES = 0, SCHED_N_SAVED_TILES = 1, SCHED_PAD_ROWS = 2, SCHED_N_PAIRS = 3, SCHED_WORDS = 8 };
 
 int sm_count();
+
+// Kernels that may run beside a grouped GEMM ask for the same shared-memory / L1 split as the GEMM (everything
+// shared): an SM only changes its split while it is idle, so a resident block with another preference keeps the
+// GEMM's thread blocks off its SM until it has finished, and the two launches run one after the other.
+template <auto Kernel>
+static inline void share_sm_with_gemm() {
+    static bool done[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+    if (!done[dev]) {
+        if (cudaFuncSetAttribute(Kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+            (void)cudaGetLastError();
+        done[dev] = true;
+    }
+}
 // Shared-memory swizzle of a tensor map: the byte span inside which TMA permutes 16-byte chunks.
 enum TmapSwizzle : int { TMAP_SWIZZLE_128B = 0, TMAP_SWIZZLE_64B = 1, TMAP_SWIZZLE_32B = 2 };
 int encode_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
