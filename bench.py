@@ -613,6 +613,13 @@ def main():
                 xb[i % 2].copy_(x_host, non_blocking=True)
             ready[i % 2].record(copy_stream)
 
+    # The loss of every step is read back inside the timed region, through pinned memory and one step late: step i's
+    # kernels are queued before the host waits for the loss of step i-1, as a training loop that logs its loss does, so
+    # the device never idles while the host queues the next step.
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
+    losses = []
+
     def step_e2e(i):
         cur = xb[i % 2]
         torch.cuda.current_stream().wait_event(ready[i % 2])
@@ -625,20 +632,30 @@ def main():
         loss = torch.linalg.vector_norm(y, dtype=torch.float32).square() / y.numel()
         loss.backward()
         consumed[i % 2].record(torch.cuda.current_stream())
-        return float(loss.item())   # device -> host read of the step's result
+        loss_host[i % 2].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host read of the step's result
+        loss_ready[i % 2].record(torch.cuda.current_stream())
+
+    def read_loss(i):
+        loss_ready[i % 2].synchronize()
+        losses.append(float(loss_host[i % 2][0]))
 
     ms_e2e = float("nan")
     if not args.no_e2e and not args.forward_only:
         prefetch(0)
         for i in range(3):
             step_e2e(i)
+            read_loss(i)
         barrier()
         e0.record()
         for i in range(3, 3 + args.steps):
             step_e2e(i)
+            if i > 3:
+                read_loss(i - 1)
+        read_loss(2 + args.steps)
         e1.record()
         barrier()
         ms_e2e = e0.elapsed_time(e1) / args.steps
+        assert len(losses) == 3 + args.steps and all(v == v for v in losses), "a step's loss was not read back"
     t = torch.tensor([ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
