@@ -283,7 +283,9 @@ class PeerExpertParallelFunction(torch.autograd.Function):
         # of the first half travel back while the GEMMs work on the second.
         chunks = bufs.forward_chunks
         if chunks is None:
-            chunks = 2 if M * K * D * 2 >= (16 << 20) else 1
+            # decided from the token count the buffers were sized for, which is the same number on every rank (ranks
+            # may bring different numbers of tokens, but all of them must take the same sequence of hand-shakes)
+            chunks = 2 if max(bufs.max_tokens, 1) * K * D * 2 >= (16 << 20) else 1
         split = Nl // 2 if (chunks == 2 and Nl >= 2) else 0
         with torch.cuda.device(dev):
             home = ops.RoutingPlan.from_topk(topk_idx, topk_w, N, D, H, 0.0)

@@ -209,6 +209,23 @@ def test_dispatch_schedule_visits_every_row_once_and_spreads_destinations(world,
                 assert len(set(w0)) == world
 
 
+@pytest.mark.parametrize("world,Nl,split", [(2, 4, 2), (8, 16, 8), (4, 3, 1), (8, 2, 1)])
+def test_two_expert_ranges_partition_the_rows_of_every_destination(world, Nl, split):
+    """ep_dispatch_rows_range / ep_pull_rows (csrc/ep.cu) visit, for destination d and local experts [lo, hi), the run
+    [pad_off[d*Nl + lo], pad_off[d*Nl + hi]) of the sender's expert-major rows with the same round-robin schedule.  The
+    two halves of a forward pass, (0, split) and (split, Nl), must together visit every row exactly once."""
+    rng = np.random.default_rng(world * 100 + Nl)
+    padded = rng.integers(0, 6, size=world * Nl) * 128               # padded rows per (global) expert, some empty
+    pad_off = np.concatenate([[0], np.cumsum(padded)])
+    seen = []
+    for lo, hi in ((0, split), (split, Nl)):
+        starts = [int(pad_off[d * Nl + lo]) for d in range(world)]
+        seg_len = [int(pad_off[d * Nl + hi]) - starts[d] for d in range(world)]
+        for _, _, d, off in _dispatch_visit_order(seg_len, rank=1 % world, warps_total=8 * world):
+            seen.append(starts[d] + off)
+    assert sorted(seen) == list(range(int(pad_off[-1])))
+
+
 def test_peer_buffers_refuse_a_second_forward_before_the_backward():
     """The peer transport's buffers hold one step at a time (host logic only; no device memory is touched here): a
     forward pass that needs a backward pass blocks the next forward until that backward pass has run or its autograd
