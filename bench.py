@@ -599,31 +599,31 @@ def main():
     layer_tflops = layer_flops / (ms * 1e-3) / 1e12
 
     # ------------------------------------------------------------------ end to end from pinned host memory
-    # Every step's input travels from pinned host memory to the device and every step's loss is read back.  Inputs are
-    # double-buffered: the copy of step i+1 runs on a copy stream while step i computes, as a data loader would do.
+    # Every step's input travels from pinned host memory to the device and every step's loss is read back, all inside
+    # the timed region.  Both are pipelined the way a training loop with a data loader and asynchronous loss logging
+    # is: inputs are copied DEPTH-1 steps ahead on a copy stream into a ring of DEPTH device buffers, and the host
+    # waits for the loss of step i-(DEPTH-1) only after it has queued step i, so neither a slow copy nor a late host
+    # leaves the device idle (with several ranks a late rank would make every other rank wait at the hand-shakes).
+    DEPTH = 3
     copy_stream = torch.cuda.Stream(device=dev)
-    xb = [x_dev, x_host.to(dev).requires_grad_(True)]
-    ready = [torch.cuda.Event(), torch.cuda.Event()]
-    consumed = [torch.cuda.Event(), torch.cuda.Event()]
+    xb = [x_dev] + [x_host.to(dev).requires_grad_(True) for _ in range(DEPTH - 1)]
+    ready = [torch.cuda.Event() for _ in range(DEPTH)]
+    consumed = [torch.cuda.Event() for _ in range(DEPTH)]
 
     def prefetch(i):
         with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(consumed[i % 2])
+            copy_stream.wait_event(consumed[i % DEPTH])     # the step that last used this buffer has finished
             with torch.no_grad():
-                xb[i % 2].copy_(x_host, non_blocking=True)
-            ready[i % 2].record(copy_stream)
+                xb[i % DEPTH].copy_(x_host, non_blocking=True)
+            ready[i % DEPTH].record(copy_stream)
 
-    # The loss of every step is read back inside the timed region, through pinned memory and one step late: step i's
-    # kernels are queued before the host waits for the loss of step i-1, as a training loop that logs its loss does, so
-    # the device never idles while the host queues the next step.
-    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(DEPTH)]
+    loss_ready = [torch.cuda.Event() for _ in range(DEPTH)]
     losses = []
 
     def step_e2e(i):
-        cur = xb[i % 2]
-        torch.cuda.current_stream().wait_event(ready[i % 2])
-        prefetch(i + 1)
+        cur = xb[i % DEPTH]
+        torch.cuda.current_stream().wait_event(ready[i % DEPTH])
         for p in moe.parameters():
             p.grad = None
         cur.grad = None
@@ -631,31 +631,36 @@ def main():
         # mean-square loss: one reduction over y (fp32 accumulation) forward, one elementwise pass backward
         loss = torch.linalg.vector_norm(y, dtype=torch.float32).square() / y.numel()
         loss.backward()
-        consumed[i % 2].record(torch.cuda.current_stream())
-        loss_host[i % 2].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host read of the step's result
-        loss_ready[i % 2].record(torch.cuda.current_stream())
+        consumed[i % DEPTH].record(torch.cuda.current_stream())
+        loss_host[i % DEPTH].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host read of the result
+        loss_ready[i % DEPTH].record(torch.cuda.current_stream())
+        prefetch(i + DEPTH)                                  # this step's buffer is refilled once the step is through
 
     def read_loss(i):
-        loss_ready[i % 2].synchronize()
-        losses.append(float(loss_host[i % 2][0]))
+        loss_ready[i % DEPTH].synchronize()
+        losses.append(float(loss_host[i % DEPTH][0]))
 
     ms_e2e = float("nan")
     if not args.no_e2e and not args.forward_only:
-        prefetch(0)
-        for i in range(3):
+        n_pre = 3
+        for i in range(DEPTH):
+            prefetch(i)
+        for i in range(n_pre):
             step_e2e(i)
             read_loss(i)
         barrier()
         e0.record()
-        for i in range(3, 3 + args.steps):
+        first, last = n_pre, n_pre + args.steps - 1
+        for i in range(first, last + 1):
             step_e2e(i)
-            if i > 3:
-                read_loss(i - 1)
-        read_loss(2 + args.steps)
+            if i - (DEPTH - 1) >= first:
+                read_loss(i - (DEPTH - 1))
+        for i in range(max(first, last - (DEPTH - 1) + 1), last + 1):
+            read_loss(i)
         e1.record()
         barrier()
         ms_e2e = e0.elapsed_time(e1) / args.steps
-        assert len(losses) == 3 + args.steps and all(v == v for v in losses), "a step's loss was not read back"
+        assert len(losses) == n_pre + args.steps and all(v == v for v in losses), "a step's loss was not read back"
     t = torch.tensor([ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
