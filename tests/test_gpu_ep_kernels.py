@@ -67,7 +67,10 @@ class _Rank:
 
 
 @pytest.mark.parametrize("M,N,K,D,H,sp,split", [(700, 12, 3, 256, 128, 0, 6), (1500, 8, 2, 384, 136, 50, 3),
-                                                 (300, 16, 4, 128, 64, 100, 8)])
+                                                 (300, 16, 4, 128, 64, 100, 8),
+                                                 # rows that are not a multiple of 32 bytes, K outside {2,4,6,8},
+                                                 # an uneven split
+                                                 (200, 6, 5, 136, 72, 50, 2)])
 def test_split_plan_ranged_dispatch_pull_and_staged_combine(env, M, N, K, D, H, sp, split):
     _lib, ops = env
     L, p, st = _lib.lib, _lib.ptr, _lib.stream_ptr
