@@ -601,10 +601,9 @@ def main():
     # ------------------------------------------------------------------ end to end from pinned host memory
     # Every step's input travels from pinned host memory to the device and every step's loss is read back, all inside
     # the timed region.  Both are pipelined the way a training loop with a data loader and asynchronous loss logging
-    # is: inputs are copied ahead on a copy stream into a ring of DEPTH device buffers (a buffer is refilled during the
-    # backward pass of the step after the one that used it), and the host waits for the loss of step i-(DEPTH-1) only
-    # after it has queued step i, so neither a slow copy nor a late host leaves the device idle (with several ranks a
-    # late rank would make every other rank wait at the hand-shakes).
+    # is: inputs are copied ahead on a copy stream into a ring of DEPTH device buffers, and the host waits for the loss
+    # of step i-(DEPTH-1) only after it has queued step i, so neither a slow copy nor a late host leaves the device
+    # idle (with several ranks a late rank would make every other rank wait at the hand-shakes).
     DEPTH = 3
     copy_stream = torch.cuda.Stream(device=dev)
     xb = [x_dev] + [x_host.to(dev).requires_grad_(True) for _ in range(DEPTH - 1)]
@@ -629,10 +628,12 @@ def main():
             p.grad = None
         cur.grad = None
         y = moe(cur)
-        # The buffer of the step before this one is refilled now, for step i + DEPTH - 1, so that the copy runs beside
-        # the backward pass's GEMMs: a host-to-device copy that runs beside the short, latency-bound kernels and
-        # hand-shakes at the beginning of a forward pass made each of them take about twice as long.
-        if i >= 1:
+        # Several ranks: the buffer of the step before this one is refilled now, for step i + DEPTH - 1, so that the
+        # copy runs beside the backward pass's GEMMs; a host-to-device copy that runs beside the short, latency-bound
+        # kernels and hand-shakes at the beginning of an expert-parallel forward pass made each of them take about
+        # twice as long.  One GPU has no hand-shakes: its copy is queued at the end of the step (below) and runs beside
+        # the router and the gather of the next one, where it costs the power-capped GEMMs nothing.
+        if world > 1 and i >= 1:
             prefetch(i - 1 + DEPTH)
         # mean-square loss: one reduction over y (fp32 accumulation) forward, one elementwise pass backward
         loss = torch.linalg.vector_norm(y, dtype=torch.float32).square() / y.numel()
@@ -640,6 +641,8 @@ def main():
         consumed[i % DEPTH].record(torch.cuda.current_stream())
         loss_host[i % DEPTH].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host read of the result
         loss_ready[i % DEPTH].record(torch.cuda.current_stream())
+        if world == 1:
+            prefetch(i + DEPTH)
 
     def read_loss(i):
         loss_ready[i % DEPTH].synchronize()
